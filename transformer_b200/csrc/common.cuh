@@ -1,0 +1,74 @@
+// Shared device helpers for the sm_100a kernels of transformer_b200.
+//
+// Conventions used by every kernel file:
+//  * activations and matrices are `T` = float (the true 32-bit path) or __nv_bfloat16 (serving);
+//    all arithmetic happens in float, one rounding to T at the store;
+//  * the residual stream, router logits, softmax statistics, norm statistics and logits are float;
+//  * every launcher is `extern "C"`, takes raw device pointers, sizes and a cudaStream_t, checks
+//    its sizes, and returns 0 or a cudaError_t / negative argument error; it never allocates.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TB_PAGE 64  // tokens in one cache page
+
+// argument errors returned by launchers (cudaError_t values are positive)
+#define TB_ERR_ARG (-1)
+#define TB_ERR_UNSUPPORTED (-2)
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    __device__ __forceinline__ static float load(const float* p) { return *p; }
+    __device__ __forceinline__ static void store(float* p, float v) { *p = v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    __device__ __forceinline__ static float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    __device__ __forceinline__ static void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p) { return Elem<T>::load(p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v) { Elem<T>::store(p, v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `red` holds at least 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+static inline int tb_last_error() { return (int)cudaGetLastError(); }

@@ -1,0 +1,81 @@
+// Embedding gather and the fused residual-add + RMSNorm.
+//
+// The residual stream is float on both paths, so the residual sum is a 32-bit sum.
+#include "common.cuh"
+
+// x[i, :] = table[tokens[i], :]   (models/llama/cuda/src/infer.rs:98-104 copies row by row)
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                             float* __restrict__ x, int d) {
+    const int i = blockIdx.x;
+    const T* src = table + (size_t)tokens[i] * d;
+    float* dst = x + (size_t)i * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = ldf(src + c);
+}
+
+// Row r = rows ? rows[i] : i.
+//   v = x[r] + (delta ? delta[r] : 0)                      float sum
+//   if (!rows && delta) x[r] = v                           the stream is updated in place
+//   y[i] = v / sqrt(mean(v^2) + eps) * w                   statistics in float, one rounding to T
+// (call sites of rms_norm: models/llama/common/src/compute.rs:207,275,362; the residual sum is the
+//  beta = 1 of the output products, :270,:330.)
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ w,
+                                   float eps, T* __restrict__ y, int d) {
+    __shared__ float red[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* xr = x + (size_t)r * d;
+    const T* dr = delta ? delta + (size_t)r * d : nullptr;
+    const bool write_back = (rows == nullptr) && (delta != nullptr);
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float v = xr[c];
+        if (dr) v += ldf(dr + c);
+        if (write_back) xr[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)d + eps);
+    T* yr = y + (size_t)i * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float v = xr[c];
+        if (dr && !write_back) v += ldf(dr + c);
+        stf(yr + c, v * rs * w[c]);
+    }
+}
+
+template <typename T>
+static int embed_launch(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
+    if (nt < 0 || d <= 0) return TB_ERR_ARG;
+    if (nt == 0) return 0;
+    embed_kernel<T><<<nt, 256, 0, s>>>(tokens, (const T*)table, x, d);
+    return tb_last_error();
+}
+template <typename T>
+static int add_rmsnorm_launch(float* x, const void* delta, const int* rows, const float* w, float eps,
+                              void* y, int n_out, int d, cudaStream_t s) {
+    if (n_out < 0 || d <= 0) return TB_ERR_ARG;
+    if (n_out == 0) return 0;
+    int threads = d >= 2048 ? 512 : 256;
+    add_rmsnorm_kernel<T><<<n_out, threads, 0, s>>>(x, (const T*)delta, rows, w, eps, (T*)y, d);
+    return tb_last_error();
+}
+
+extern "C" {
+int tb_embed_f32(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
+    return embed_launch<float>(tokens, table, x, nt, d, s);
+}
+int tb_embed_bf16(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
+    return embed_launch<__nv_bfloat16>(tokens, table, x, nt, d, s);
+}
+int tb_add_rmsnorm_f32(float* x, const void* delta, const int* rows, const float* w, float eps, void* y,
+                       int n_out, int d, cudaStream_t s) {
+    return add_rmsnorm_launch<float>(x, delta, rows, w, eps, y, n_out, d, s);
+}
+int tb_add_rmsnorm_bf16(float* x, const void* delta, const int* rows, const float* w, float eps, void* y,
+                        int n_out, int d, cudaStream_t s) {
+    return add_rmsnorm_launch<__nv_bfloat16>(x, delta, rows, w, eps, y, n_out, d, s);
+}
+}

@@ -1,0 +1,102 @@
+"""The compiled kernels as Python callables (ctypes over the library's ``extern "C"`` launchers).
+
+Every launcher returns 0 or an error code; :func:`call` turns a code into an exception that names
+the launcher.  Pointers are passed as integers (``tensor.data_ptr()``), and the last argument of
+every launcher is the CUDA stream, taken from torch's current stream, so kernels run (and are
+captured into CUDA graphs) in order with torch's own work.
+
+The library is loaded on first use and the process fails loudly when it cannot be built or loaded:
+there is no CPU path and no library fallback behind these functions.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict
+
+import torch
+
+from .build import KernelBuildError, ensure_built
+
+_P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+_CODES = {"p": _P, "i": _I, "f": _F, "l": _L}
+
+# name -> argument codes (the trailing stream is added for all but the ones marked no_stream)
+_SIGNATURES: Dict[str, str] = {
+    "tb_embed_f32": "pppii", "tb_embed_bf16": "pppii",
+    "tb_add_rmsnorm_f32": "ppppfpii", "tb_add_rmsnorm_bf16": "ppppfpii",
+    "tb_rope_cache_f32": "ppppippppiiiii", "tb_rope_cache_bf16": "ppppippppiiiii",
+    "tb_attention_f32": "ppppppppppiiiiiiiif", "tb_attention_bf16": "ppppppppppiiiiiiiif",
+    "tb_gemm_simt_f32": "pppppliiiiiiii".replace(" ", ""), "tb_gemm_simt_bf16": "pppppliiiiiiii",
+    "tb_router_f32": "pppppiiii", "tb_router_bf16": "pppppiiii",
+    "tb_moe_dispatch": "ppppiii",
+    "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
+    "tb_sample": "plpiififpp",
+}
+_NO_STREAM = {"tb_attention_tile_tokens": "ii"}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = ensure_built()
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:  # pragma: no cover
+                raise KernelBuildError(f"cannot load {path}: {e}") from e
+            for name, codes in _SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.argtypes = [_CODES[c] for c in codes] + [_P]
+                fn.restype = _I
+            for name, codes in _NO_STREAM.items():
+                fn = getattr(lib, name)
+                fn.argtypes = [_CODES[c] for c in codes]
+                fn.restype = _I
+            _lib = lib
+    return _lib
+
+
+def library_path() -> str:
+    return ensure_built()
+
+
+def _error_text(code: int) -> str:
+    if code == -1:
+        return "bad argument"
+    if code == -2:
+        return "size not supported by this kernel"
+    return f"CUDA error {code}"
+
+
+def call(name: str, *args) -> None:
+    """Launch ``name`` on torch's current stream."""
+    fn = getattr(library(), name)
+    rc = fn(*args, torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise KernelError(f"{name}: {_error_text(rc)}")
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def suffix(dtype: torch.dtype) -> str:
+    if dtype == torch.float32:
+        return "f32"
+    if dtype == torch.bfloat16:
+        return "bf16"
+    raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
+
+
+def attention_tile_tokens(nh: int, nkvh: int) -> int:
+    return library().tb_attention_tile_tokens(nh, nkvh)

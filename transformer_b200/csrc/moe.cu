@@ -1,0 +1,165 @@
+// Mixture-of-experts routing on the device: router logits + top-k + weights, the token -> expert
+// dispatch lists, and the weighted combine.
+//
+// The reference copies the router logits to the host in every layer, sorts them there and then
+// loops over tokens and experts (models/llama/common/src/compute.rs:294-333,375-394).  Here nothing
+// leaves the device: a step has no synchronisation point.
+#include "common.cuh"
+
+#define ROUTER_WARPS 4
+#define ROUTER_MAX_E 1024
+
+// One warp per token.
+//   logits[e] = x1 . Wr[e]                       float accumulation, kept in float
+//   keep the k largest, ties to the lower expert (the reference sorts descending, compute.rs:381)
+//   w_j = exp(v_j - v_0) / sum_kept exp(v_i - v_0)    softmax over the kept logits (compute.rs:383-392)
+// topk_idx / topk_w are in descending-logit order.
+template <typename T>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restrict__ topk_idx,
+              float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d, int E, int k) {
+    extern __shared__ float sm[];   // [ROUTER_WARPS][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * ROUTER_WARPS + warp;
+    if (t >= nt) return;
+    float* lg = sm + warp * E;
+    const T* xr = x1 + (size_t)t * d;
+    for (int e = 0; e < E; ++e) {
+        const T* w = wr + (size_t)e * d;
+        float acc = 0.f;
+        for (int c = lane; c < d; c += 32) acc += ldf(xr + c) * ldf(w + c);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            lg[e] = acc;
+            if (logits_out) logits_out[(size_t)t * E + e] = acc;
+        }
+    }
+    __syncwarp();
+    float v0 = 0.f, sum = 0.f;
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = lg[e];
+            if (v > best) {   // strictly greater: the lower index stays on ties (e ascends)
+                best = v;
+                bi = e;
+            }
+        }
+        // never-chosen sentinel: an expert already taken is marked by NaN below
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (bi >= E) bi = 0;   // only when every remaining logit is -inf or NaN
+        if (j == 0) v0 = best;
+        const float p = expf(best - v0);
+        sum += p;
+        if (lane == 0) {
+            topk_idx[(size_t)t * k + j] = bi;
+            topk_w[(size_t)t * k + j] = p;
+            lg[bi] = __int_as_float(0x7fc00000);   // NaN compares false with everything: taken
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / sum;
+    for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] *= inv;
+}
+
+// One block builds the dispatch lists for M = nt * k (token, choice) pairs:
+//   group_offsets[e] .. group_offsets[e+1]   rows of expert e in the sorted order
+//   sorted_token[r]                          token whose activation row r reads
+//   pair_row[t * k + j]                      row r that holds the pair's result
+// The order of the rows inside one expert is not fixed; no result depends on it (every row of a
+// product is computed alone, and the combine reads rows through pair_row in the order of j).
+__global__ void __launch_bounds__(1024)
+moe_dispatch_kernel(const int* __restrict__ topk_idx, int* __restrict__ group_offsets,
+                    int* __restrict__ sorted_token, int* __restrict__ pair_row, int M, int k, int E) {
+    __shared__ int count[ROUTER_MAX_E + 1];
+    __shared__ int cursor[ROUTER_MAX_E];
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < M; p += blockDim.x) atomicAdd(&count[topk_idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = count[e];
+            cursor[e] = run;
+            group_offsets[e] = run;
+            run += c;
+        }
+        group_offsets[E] = run;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < M; p += blockDim.x) {
+        const int r = atomicAdd(&cursor[topk_idx[p]], 1);
+        sorted_token[r] = p / k;
+        pair_row[p] = r;
+    }
+}
+
+// delta[t, :] = sum_j w[t, j] * y[pair_row[t, j], :]   in float, j ascending = descending logit,
+// the order in which the reference accumulates the experts (compute.rs:319-330); one rounding.
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ pair_row,
+                                   const float* __restrict__ topk_w, T* __restrict__ delta, int d, int k) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < k; ++j)
+            acc += topk_w[(size_t)t * k + j] * ldf(y + (size_t)pair_row[(size_t)t * k + j] * d + c);
+        stf(delta + (size_t)t * d + c, acc);
+    }
+}
+
+template <typename T>
+static int router_launch(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt,
+                         int d, int E, int k, cudaStream_t s) {
+    if (nt < 0 || d <= 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
+    if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
+    if (nt == 0) return 0;
+    const int blocks = (nt + ROUTER_WARPS - 1) / ROUTER_WARPS;
+    router_kernel<T><<<blocks, ROUTER_WARPS * 32, (size_t)ROUTER_WARPS * E * sizeof(float), s>>>(
+        (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k);
+    return tb_last_error();
+}
+template <typename T>
+static int combine_launch(const void* y, const int* pair_row, const float* topk_w, void* delta, int nt, int d,
+                          int k, cudaStream_t s) {
+    if (nt < 0 || d <= 0 || k <= 0) return TB_ERR_ARG;
+    if (nt == 0) return 0;
+    moe_combine_kernel<T><<<nt, 256, 0, s>>>((const T*)y, pair_row, topk_w, (T*)delta, d, k);
+    return tb_last_error();
+}
+
+extern "C" {
+int tb_router_f32(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt, int d,
+                  int E, int k, cudaStream_t s) {
+    return router_launch<float>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k, s);
+}
+int tb_router_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt, int d,
+                   int E, int k, cudaStream_t s) {
+    return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k, s);
+}
+int tb_moe_dispatch(const int* topk_idx, int* group_offsets, int* sorted_token, int* pair_row, int M, int k, int E,
+                    cudaStream_t s) {
+    if (M < 0 || k <= 0 || E <= 0) return TB_ERR_ARG;
+    if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
+    moe_dispatch_kernel<<<1, 1024, 0, s>>>(topk_idx, group_offsets, sorted_token, pair_row, M, k, E);
+    return tb_last_error();
+}
+int tb_moe_combine_f32(const void* y, const int* pair_row, const float* topk_w, void* delta, int nt, int d, int k,
+                       cudaStream_t s) {
+    return combine_launch<float>(y, pair_row, topk_w, delta, nt, d, k, s);
+}
+int tb_moe_combine_bf16(const void* y, const int* pair_row, const float* topk_w, void* delta, int nt, int d, int k,
+                        cudaStream_t s) {
+    return combine_launch<__nv_bfloat16>(y, pair_row, topk_w, delta, nt, d, k, s);
+}
+}

@@ -1,0 +1,83 @@
+// Rotary position encoding of q and k, fused with the write of k and v into the paged cache.
+//
+// qkv is [nt, (nh + 2 nkvh) dh] with the heads ordered q, k, v
+// (models/llama/common/src/compute.rs:225-227).  q is rotated in place; k is rotated and stored,
+// v is copied, into the page that holds the token's position
+// (the reference stores k, v at pos..pos+seq of the request's cache, compute.rs:244-263).
+// Angles come from a float table [positions, dh/2] built on the host in double precision:
+// angle(p, i) = p * theta^(-2i/dh).
+//
+// Cache of one layer: K and V each [pages, nkvh, TB_PAGE, dh].
+#include "common.cuh"
+
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ tok_seq,
+                                  const int* __restrict__ tok_pos, const int* __restrict__ page_table,
+                                  int max_pages, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
+                                  int nh, int nkvh, int dh, int half_pairing) {
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = dh >> 1;
+    T* row = qkv + (size_t)t * (nh + 2 * nkvh) * dh;
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+    size_t cache_row = 0;
+    if (kc) {
+        const int page = page_table[(size_t)tok_seq[t] * max_pages + pos / TB_PAGE];
+        cache_row = ((size_t)page * nkvh * TB_PAGE + (pos % TB_PAGE)) * dh;  // + g * TB_PAGE * dh
+    }
+    const int n_rot = (nh + nkvh) * half;
+    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const int i0 = half_pairing ? i : 2 * i;
+        const int i1 = half_pairing ? i + half : 2 * i + 1;
+        T* h = row + (size_t)head * dh;
+        const float x0 = ldf(h + i0), x1 = ldf(h + i1);
+        const float c = cs[i], s = sn[i];
+        const float y0 = x0 * c - x1 * s;
+        const float y1 = x0 * s + x1 * c;
+        if (head < nh) {
+            stf(h + i0, y0);
+            stf(h + i1, y1);
+        } else if (kc) {
+            T* dst = kc + cache_row + (size_t)(head - nh) * TB_PAGE * dh;
+            stf(dst + i0, y0);
+            stf(dst + i1, y1);
+        }
+    }
+    if (vc) {
+        const T* v = row + (size_t)(nh + nkvh) * dh;
+        for (int idx = threadIdx.x; idx < nkvh * dh; idx += blockDim.x) {
+            const int g = idx / dh, c = idx - g * dh;
+            vc[cache_row + (size_t)g * TB_PAGE * dh + c] = v[idx];
+        }
+    }
+}
+
+template <typename T>
+static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, const int* page_table,
+                             int max_pages, const float* cos_t, const float* sin_t, void* kc, void* vc,
+                             int nt, int nh, int nkvh, int dh, int half_pairing, cudaStream_t s) {
+    if (nt < 0 || nh <= 0 || nkvh <= 0 || dh <= 0 || (dh & 1)) return TB_ERR_ARG;
+    if ((kc == nullptr) != (vc == nullptr)) return TB_ERR_ARG;
+    if (nt == 0) return 0;
+    rope_cache_kernel<T><<<nt, 256, 0, s>>>((T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
+                                            (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
+    return tb_last_error();
+}
+
+extern "C" {
+int tb_rope_cache_f32(void* qkv, const int* tok_seq, const int* tok_pos, const int* page_table, int max_pages,
+                      const float* cos_t, const float* sin_t, void* kc, void* vc, int nt, int nh, int nkvh,
+                      int dh, int half_pairing, cudaStream_t s) {
+    return rope_cache_launch<float>(qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t, kc, vc, nt, nh,
+                                    nkvh, dh, half_pairing, s);
+}
+int tb_rope_cache_bf16(void* qkv, const int* tok_seq, const int* tok_pos, const int* page_table, int max_pages,
+                       const float* cos_t, const float* sin_t, void* kc, void* vc, int nt, int nh, int nkvh,
+                       int dh, int half_pairing, cudaStream_t s) {
+    return rope_cache_launch<__nv_bfloat16>(qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t, kc, vc,
+                                            nt, nh, nkvh, dh, half_pairing, s);
+}
+}

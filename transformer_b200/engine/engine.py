@@ -1,0 +1,198 @@
+"""The model on the device and its one step function.
+
+:class:`Engine` = the parts built from a :class:`~transformer_b200.parts.spec.ModelSpec` + the
+weights bound to them + the cache + scratch memory.  :meth:`Engine.step` is the only way tokens
+reach the model: generation, trace replay and the benchmarks all call it.
+
+The reference's step is ``LlamaWorker::launch`` (models/llama/common/src/compute.rs:139-366): a
+ragged batch of requests {cache, seq_len, out_len, pos}, embeddings in, logits of the last
+``out_len`` rows of each request out.  Differences by design: token ids in (the gather is a
+kernel), positions come from the cache's own bookkeeping, any rows may be asked for, the logits
+are always float, and nothing inside synchronises with the host.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.paged import Cache
+from ..cache.slots import CacheError
+from ..csrc import lib
+from ..parts.block import Layer
+from ..parts.base import NORMS
+from ..parts.linear import matmul_nt
+from ..parts.spec import ModelSpec
+from .context import StepContext, Workspace
+
+
+class StepError(ValueError):
+    pass
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, weights: Dict[tuple, torch.Tensor], dtype: torch.dtype,
+                 device: torch.device, *, max_tokens: int, max_slots: Optional[int] = None,
+                 max_step_tokens: int = 8192):
+        if device.type != "cuda":
+            raise RuntimeError("transformer_b200 runs on a CUDA device only; there is no CPU path")
+        lib.library()   # fail now, loudly, if the kernels cannot be built or loaded
+        spec.validate()
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.max_step_tokens = int(max_step_tokens)
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        self.layers: List[Layer] = [Layer(ls, dtype, device) for ls in spec.layers]
+        self.final_norm = NORMS.build(spec.final_norm, dtype, device)
+        self._bind(weights)
+        runs = spec.order
+        mixers = [self.layers[e.layer].mixer for e in runs]
+        self.cache = Cache([m.cache_need() for m in mixers], [m.state_need() for m in mixers],
+                           [e.cache_of for e in runs], max_tokens=max_tokens, max_context=spec.max_context,
+                           max_slots=max_slots, dtype=dtype, device=device)
+        self.workspace = Workspace(device)
+        self._identity_tables = {}
+        self._tile_sizes = sorted({lib.attention_tile_tokens(m.nh, m.nkvh) for m in mixers
+                                   if hasattr(m, "nh") and hasattr(m, "nkvh")})
+        self._staging = []
+        self._staging_next = 0
+        self._staging_dev = None
+
+    # ---- construction ---------------------------------------------------------------------
+    def _bind(self, weights) -> None:
+        self.embedding = weights[("embedding", "table")]
+        self.head = weights[("head", "weight")]
+        V, d = self.spec.vocab, self.spec.width
+        for name, t in (("embedding", self.embedding), ("head", self.head)):
+            if tuple(t.shape) != (V, d):
+                raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {(V, d)}")
+        for i, layer in enumerate(self.layers):
+            for pname, part in layer.parts().items():
+                part.bind({n: weights[("layers", i, pname, n)] for n in part.parameters()})
+        self.final_norm.bind({n: weights[("final_norm", n)] for n in self.final_norm.parameters()})
+
+    def staging(self, n_ints: int):
+        """A pinned host buffer, the device buffer it is copied to, and the event of its last copy."""
+        size = max(4096, 1 << (int(n_ints) - 1).bit_length())
+        if not self._staging or self._staging[0][0].numel() < size:
+            torch.cuda.synchronize(self.device)
+            self._staging = [(torch.empty(size, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                             for _ in range(4)]
+            self._staging_dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        host, event = self._staging[self._staging_next]
+        self._staging_next = (self._staging_next + 1) % len(self._staging)
+        return host, self._staging_dev, event
+
+    # ---- sequences ------------------------------------------------------------------------
+    def open(self) -> int:
+        """A slot for a new sequence."""
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        """Give back what the sequence holds."""
+        self.cache.close(slot)
+
+    # ---- the step ---------------------------------------------------------------------------
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """Run the given next tokens of the given sequences as one batch, from the cache.
+
+        slots[b]: an open slot; tokens[b]: its next tokens (one or many, lengths may differ);
+        want[b]: indices into tokens[b] whose logits are wanted (default: the last).  Returns float
+        logits [sum of len(want[b]), vocab] on the device, in the order of the batch and of ``want``.
+        """
+        B = len(slots)
+        if len(tokens) != B:
+            raise StepError(f"{B} slots but {len(tokens)} token lists")
+        if want is None:
+            want = [[len(t) - 1] for t in tokens]
+        if len(want) != B:
+            raise StepError(f"{B} slots but {len(want)} want lists")
+        if len(set(slots)) != B:
+            raise StepError("a slot appears twice in one step")
+        V = self.spec.vocab
+        for b in range(B):
+            n = len(tokens[b])
+            if n == 0:
+                raise StepError(f"sequence {b} of the step brings no token")
+            for t in tokens[b]:
+                if not (0 <= int(t) < V):
+                    raise StepError(f"token {t} lies outside the vocabulary of {V}")
+            for w in want[b]:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"wanted place {w} lies outside the {n} tokens of sequence {b}")
+        # room for everything first: a step either runs whole or not at all
+        need = sum(self.cache.table.pages_needed(s, len(t)) for s, t in zip(slots, tokens))
+        if need > self.cache.table.pages.free:
+            raise CacheError(f"cache full: the step needs {need} more pages, {self.cache.table.pages.free} are free")
+        for s, t in zip(slots, tokens):
+            if self.cache.length(s) + len(t) > self.spec.max_context:
+                raise CacheError(f"slot {s} would exceed the context of {self.spec.max_context}")
+        pos0 = [self.cache.extend(s, len(t)) for s, t in zip(slots, tokens)]
+
+        n_total = sum(len(t) for t in tokens)
+        if n_total <= self.max_step_tokens:
+            rows, base = [], 0
+            for b in range(B):
+                rows.extend(base + int(w) for w in want[b])
+                base += len(tokens[b])
+            return self._run(slots, tokens, pos0, rows)
+        return self._run_in_pieces(slots, tokens, pos0, want)
+
+    def _run_in_pieces(self, slots, tokens, pos0, want) -> torch.Tensor:
+        """A step larger than the scratch memory allows runs as consecutive pieces of the token
+        axis; a sequence cut by a piece boundary continues from the cache in the next piece."""
+        n_want = sum(len(w) for w in want)
+        out = torch.empty((n_want, self.spec.vocab), dtype=torch.float32, device=self.device)
+        # where each wanted row goes in `out`
+        order, k = {}, 0
+        for b in range(len(slots)):
+            for w in want[b]:
+                order.setdefault((b, int(w)), []).append(k)
+                k += 1
+        cur = [0] * len(slots)
+        b = 0
+        while b < len(slots):
+            p_slots, p_tokens, p_pos0, p_rows, p_dest, room, base = [], [], [], [], [], self.max_step_tokens, 0
+            while b < len(slots) and room > 0:
+                take = min(room, len(tokens[b]) - cur[b])
+                lo, hi = cur[b], cur[b] + take
+                p_slots.append(slots[b])
+                p_tokens.append(tokens[b][lo:hi])
+                p_pos0.append(pos0[b] + lo)
+                for i in range(lo, hi):
+                    for dest in order.get((b, i), ()):
+                        p_rows.append(base + i - lo)
+                        p_dest.append(dest)
+                base += take
+                room -= take
+                cur[b] = hi
+                if hi == len(tokens[b]):
+                    b += 1
+            logits = self._run(p_slots, p_tokens, p_pos0, p_rows)
+            if p_dest:
+                out[torch.tensor(p_dest, device=self.device)] = logits
+        return out
+
+    def _run(self, slots, tokens, pos0, rows, *, fixed_pages=None, logits_out=None) -> torch.Tensor:
+        ctx = StepContext(self, slots, tokens, pos0, rows, self._tile_sizes, fixed_pages=fixed_pages)
+        return self._forward(ctx, logits_out)
+
+    def _forward(self, ctx: StepContext, logits_out=None) -> torch.Tensor:
+        nt, d, V = ctx.nt, self.spec.width, self.spec.vocab
+        sfx = lib.suffix(self.dtype)
+        x = ctx.scratch("stream", (nt, d), torch.float32)
+        lib.call("tb_embed_" + sfx, lib.ptr(ctx.tok_ids), lib.ptr(self.embedding), lib.ptr(x), nt, d)
+        pending = None
+        for r, entry in enumerate(self.spec.order):
+            layer = self.layers[entry.layer]
+            pending = layer.forward(ctx, x, pending, self.cache.view(r), self.cache.state_of(r))
+        n_out = len(ctx.h_want)
+        logits = logits_out if logits_out is not None else \
+            torch.empty((n_out, V), dtype=torch.float32, device=self.device)
+        if n_out:
+            xn = ctx.scratch("final.xn", (n_out, d), self.dtype)
+            self.final_norm.forward(ctx, x, pending, ctx.want_rows, xn)
+            matmul_nt(xn, self.head, logits)
+        return logits

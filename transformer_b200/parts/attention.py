@@ -1,0 +1,74 @@
+"""Grouped-query attention over the paged cache (models/llama/common/src/compute.rs:210-270).
+
+qkv = x1 Wqkv^T (one merged product, heads ordered q, k, v); rotary encoding of q and k fused with
+the write of k and v into the cache; causal attention of the step's tokens over everything their
+sequences hold; out = o Wo^T.  The residual sum is the caller's (the block's) business.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..csrc import lib
+from .base import MIXERS, POSITIONS, CacheNeed, Mixer, ParamDecl
+from .linear import matmul_nt
+from .spec import PartSpec
+
+
+@MIXERS.register("attention")
+class Attention(Mixer):
+    """params: width, nh, nkvh, dh, position (a PartSpec of a rotary encoding, or None)."""
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.d = int(params["width"])
+        self.nh = int(params["nh"])
+        self.nkvh = int(params["nkvh"])
+        self.dh = int(params["dh"])
+        if self.nh % self.nkvh:
+            raise ValueError(f"{self.nh} heads cannot share {self.nkvh} key/value heads")
+        if self.dh % 16 or self.dh > 256:
+            raise ValueError(f"the attention kernels take head sizes 16, 32, ..., 256; got {self.dh}")
+        pos = params.get("position")
+        self.position = POSITIONS.build(pos, dtype, device) if isinstance(pos, PartSpec) else None
+        self.qkv_width = (self.nh + 2 * self.nkvh) * self.dh
+        self.scale = 1.0 / math.sqrt(self.dh)
+        self.tile_tokens = None
+
+    def parameters(self):
+        return {
+            "wqkv": ParamDecl((self.qkv_width, self.d)),
+            "wo": ParamDecl((self.d, self.nh * self.dh)),
+        }
+
+    def cache_need(self):
+        return CacheNeed("full", self.nkvh, self.dh)
+
+    def forward(self, ctx, x1, out, cache, state) -> None:
+        nt = x1.shape[0]
+        sfx = lib.suffix(self.dtype)
+        qkv = ctx.scratch("attn.qkv", (nt, self.qkv_width), self.dtype)
+        matmul_nt(x1, self.weights["wqkv"], qkv)
+        table = ctx.page_table(cache)
+        if self.position is not None:
+            cos, sin = self.position.tables()
+            half = self.position.half_pairing
+        else:
+            cos, sin = ctx.identity_rotation(self.dh)
+            half = 0
+        kc, vc = (cache.k, cache.v) if cache.writable else (None, None)
+        lib.call("tb_rope_cache_" + sfx, lib.ptr(qkv), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos),
+                 lib.ptr(table), ctx.max_pages, lib.ptr(cos), lib.ptr(sin), lib.ptr(kc), lib.ptr(vc),
+                 nt, self.nh, self.nkvh, self.dh, half)
+        o = ctx.scratch("attn.o", (nt, self.nh * self.dh), self.dtype)
+        tiles = ctx.attention_tiles(self.nh, self.nkvh)
+        splits = ctx.attention_splits(tiles.count, self.nh, self.nkvh)
+        partial = None
+        if splits > 1:
+            partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
+        lib.call("tb_attention_" + sfx, lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                 lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
+                 lib.ptr(partial), tiles.count, nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh,
+                 splits, self.scale)
+        matmul_nt(o, self.weights["wo"], out)

@@ -1,0 +1,128 @@
+"""Interfaces of the parts a layer is put together from, and one registry per kind of part.
+
+A part is built from the parameters of its :class:`~transformer_b200.parts.spec.PartSpec` alone; it
+does not know which model it is in, which layer it is, or what the other parts are.  The engine
+talks to parts only through the methods below.
+
+============  ===================================================================================
+kind          interface
+============  ===================================================================================
+Norm          ``forward(ctx, x, delta, rows, y)``: ``v = x[rows] + delta[rows]`` (float sum; written
+              back to ``x`` when ``rows`` is None), ``y = norm(v)``.  ``x`` is the float residual
+              stream, ``delta`` the previous part's output or None.
+Mixer         ``forward(ctx, x1, out, cache, state)``: reads the normed activations ``x1`` [nt, d]
+              and writes its contribution to the stream into ``out`` [nt, d].  ``cache`` is the
+              run's :class:`~transformer_b200.cache.paged.CacheView` (None if ``cache_need()``
+              is None), ``state`` its per-sequence state tensor [slots, *shape] (None if
+              ``state_need()`` is None); rows of ``state`` are addressed by ``ctx.slots``.
+FeedForward   ``forward(ctx, x1, out)``.
+Position      owned by the mixer that uses it; for rotary encodings ``tables()`` gives cos and sin.
+============  ===================================================================================
+
+All parts declare their parameters with :meth:`Part.parameters` (name -> shape, role, init) and
+receive the device tensors with :meth:`Part.bind`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamDecl:
+    shape: Tuple[int, ...]
+    role: str = "matrix"     # "matrix" | "norm" | "table"
+    init: str = "normal"     # "normal" | "ones"
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """Keys and values of every position ("full") for nkvh heads of size dh."""
+    kind: str
+    nkvh: int
+    dh: int
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A tensor of fixed size per sequence, zero when a sequence starts."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    def __init__(self, params: Dict[str, Any], dtype: torch.dtype, device: torch.device):
+        self.params = dict(params)
+        self.dtype = dtype
+        self.device = device
+        self.weights: Dict[str, torch.Tensor] = {}
+
+    def parameters(self) -> Dict[str, ParamDecl]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        decl = self.parameters()
+        for name, d in decl.items():
+            t = tensors[name]
+            if tuple(t.shape) != tuple(d.shape):
+                raise ValueError(f"{type(self).__name__}.{name}: shape {tuple(t.shape)}, expected {d.shape}")
+        self.weights = {n: tensors[n] for n in decl}
+
+
+class Norm(Part):
+    def forward(self, ctx, x, delta, rows, y) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, ctx, x1, out, cache, state) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x1, out) -> None:
+        raise NotImplementedError
+
+
+class Position(Part):
+    pass
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: Dict[str, Callable] = {}
+
+    def register(self, kind: str, cls=None, *, replace: bool = False):
+        def deco(c):
+            if kind in self._kinds and not replace:
+                raise ValueError(f"{self.what} kind {kind!r} is already registered")
+            self._kinds[kind] = c
+            return c
+        return deco(cls) if cls is not None else deco
+
+    def unregister(self, kind: str) -> None:
+        self._kinds.pop(kind, None)
+
+    def build(self, spec, dtype, device):
+        cls = self._kinds.get(spec.kind)
+        if cls is None:
+            raise ValueError(f"unknown {self.what} kind {spec.kind!r}; registered: {sorted(self._kinds)}")
+        return cls(spec.get(), dtype, device)
+
+    def kinds(self):
+        return sorted(self._kinds)
+
+
+NORMS = Registry("norm")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+POSITIONS = Registry("position encoding")

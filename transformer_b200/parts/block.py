@@ -1,0 +1,42 @@
+"""The arrangement of a layer's parts in a block.
+
+"pre_norm" (models/llama/common/src/compute.rs:204-336):
+
+    x += mixer(norm_m(x));   x += feed_forward(norm_f(x))
+
+The residual stream ``x`` is float.  A part writes its contribution ``delta``; the sum into ``x``
+is fused into the NEXT norm (of this block or the following one, or the final norm), so a block
+takes the pending delta of the block before it and returns its own.
+"""
+from __future__ import annotations
+
+from .base import FEED_FORWARDS, MIXERS, NORMS
+
+
+class Layer:
+    """The parts of one LayerSpec, built."""
+
+    def __init__(self, spec, dtype, device):
+        if spec.arrangement != "pre_norm":
+            raise ValueError(f"unknown block arrangement {spec.arrangement!r}")
+        self.spec = spec
+        self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, dtype, device)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, dtype, device)
+
+    def parts(self):
+        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
+                "feed_forward_norm": self.feed_forward_norm, "feed_forward": self.feed_forward}
+
+    def forward(self, ctx, x, pending, cache_view, state):
+        """x: float [nt, d]; pending: the previous block's delta or None.  Returns this block's
+        pending delta (the feed-forward's output)."""
+        nt, d = x.shape
+        x1 = ctx.scratch("block.x1", (nt, d), ctx.dtype)
+        self.mixer_norm.forward(ctx, x, pending, None, x1)
+        delta = ctx.scratch("block.delta", (nt, d), ctx.dtype)
+        self.mixer.forward(ctx, x1, delta, cache_view, state)
+        self.feed_forward_norm.forward(ctx, x, delta, None, x1)
+        self.feed_forward.forward(ctx, x1, delta)
+        return delta

@@ -1,0 +1,87 @@
+"""Feed-forward parts: a dense SwiGLU and a softmax-top-k mixture of SwiGLU experts.
+
+The reference runs the experts as a host loop over tokens and chosen experts with one product
+each and a device-to-host copy of the router logits in every layer
+(models/llama/common/src/compute.rs:294-333).  Here the tokens are sorted by expert on the device
+and every expert runs once over all of its tokens (a grouped product); nothing touches the host.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import lib
+from .base import FEED_FORWARDS, FeedForward, ParamDecl
+from .linear import gemm_simt, matmul_nt
+
+
+@FEED_FORWARDS.register("swiglu")
+class DenseSwiGLU(FeedForward):
+    """params: width, di.  gate_up = x1 Wgu^T (gate rows first), h = silu(gate) * up, out = h Wd^T
+    (compute.rs:278-292)."""
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.d = int(params["width"])
+        self.di = int(params["di"])
+
+    def parameters(self):
+        return {"wgu": ParamDecl((2 * self.di, self.d)), "wd": ParamDecl((self.d, self.di))}
+
+    def forward(self, ctx, x1, out) -> None:
+        nt = x1.shape[0]
+        h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
+        gemm_simt(x1, self.weights["wgu"], h, out_kind=2)
+        matmul_nt(h, self.weights["wd"], out)
+
+
+@FEED_FORWARDS.register("moe")
+class MoE(FeedForward):
+    """params: width, di, nexp, nexp_use.
+
+    router logits (float) -> the nexp_use largest, equal logits to the lower expert -> softmax over
+    the kept logits (compute.rs:375-394) -> expert SwiGLU (compute.rs:320-328) -> weighted sum in
+    descending-logit order, in float (compute.rs:329-330)."""
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.d = int(params["width"])
+        self.di = int(params["di"])
+        self.E = int(params["nexp"])
+        self.k = int(params["nexp_use"])
+        if not (0 < self.k <= self.E):
+            raise ValueError(f"experts per token {self.k} must lie in 1..{self.E}")
+        if self.E > 1024:
+            raise ValueError(f"the routing kernels take up to 1024 experts, got {self.E}")
+
+    def parameters(self):
+        return {
+            "router": ParamDecl((self.E, self.d)),
+            "wgu": ParamDecl((self.E, 2 * self.di, self.d)),
+            "wd": ParamDecl((self.E, self.d, self.di)),
+        }
+
+    def route(self, ctx, x1, logits_out=None):
+        nt = x1.shape[0]
+        idx = ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32)
+        w = ctx.scratch("moe.topk_w", (nt, self.k), torch.float32)
+        lib.call("tb_router_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
+                 lib.ptr(idx), lib.ptr(w), lib.ptr(logits_out), nt, self.d, self.E, self.k)
+        return idx, w
+
+    def forward(self, ctx, x1, out) -> None:
+        nt = x1.shape[0]
+        M = nt * self.k
+        sfx = lib.suffix(self.dtype)
+        idx, w = self.route(ctx, x1)
+        offsets = ctx.scratch("moe.offsets", (self.E + 1,), torch.int32)
+        sorted_token = ctx.scratch("moe.sorted_token", (M,), torch.int32)
+        pair_row = ctx.scratch("moe.pair_row", (M,), torch.int32)
+        lib.call("tb_moe_dispatch", lib.ptr(idx), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
+                 M, self.k, self.E)
+        h = ctx.scratch("moe.h", (M, self.di), self.dtype)
+        gemm_simt(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
+                  out_kind=2)
+        y = ctx.scratch("moe.y", (M, self.d), self.dtype)
+        gemm_simt(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E, out_kind=0)
+        lib.call("tb_moe_combine_" + sfx, lib.ptr(y), lib.ptr(pair_row), lib.ptr(w), lib.ptr(out), nt, self.d,
+                 self.k)
