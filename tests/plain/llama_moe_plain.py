@@ -151,13 +151,27 @@ def expert_ffn(x1_tok, w_gate_up, w_down) -> torch.Tensor:
     return w_down @ (silu(gu[:di]) * gu[di:])
 
 
-def moe_feed_forward(x1, w_router, w_gate_up_exps, w_down_exps, k: int) -> torch.Tensor:
+def moe_feed_forward(x1, w_router, w_gate_up_exps, w_down_exps, k: int, forced=None, margins=None) -> torch.Tensor:
     """For every token: router logits, top-k with softmax over the kept logits, the weighted sum of
-    the kept experts in descending-logit order (models/llama/common/src/compute.rs:294-333)."""
+    the kept experts in descending-logit order (models/llama/common/src/compute.rs:294-333).
+
+    Two aids for comparing with an implementation that rounds differently (top-k is discontinuous:
+    a near-tie may fall the other way): ``forced[a]`` replaces token a's free choice by a given set
+    of experts (weights still from this function's own logits), and ``margins`` collects per token
+    (free choice, gap between the k-th and (k+1)-th logit, largest |logit|)."""
     out = torch.zeros_like(x1)
     for a in range(x1.shape[0]):
         logits = w_router @ x1[a]
         experts, weights = route(logits, k)
+        if margins is not None:
+            srt = sorted((float(v) for v in logits), reverse=True)
+            gap = srt[k - 1] - srt[k] if k < len(srt) else float("inf")
+            margins.append((list(experts), gap, max(abs(srt[0]), abs(srt[-1]))))
+        if forced is not None and set(forced[a]) != set(experts):
+            experts = sorted((int(e) for e in forced[a]), key=lambda e: (-float(logits[e]), e))
+            kept = torch.stack([logits[e] for e in experts])
+            weights = torch.exp(kept - kept[0])
+            weights = weights / weights.sum()
         for e, w in zip(experts, weights):
             out[a] += w * expert_ffn(x1[a], w_gate_up_exps[e], w_down_exps[e])
     return out
@@ -168,7 +182,7 @@ def dense_feed_forward(x1, w_gate_up, w_down) -> torch.Tensor:
     return torch.stack([expert_ffn(x1[a], w_gate_up, w_down) for a in range(x1.shape[0])])
 
 
-def block(x, t: Dict[str, torch.Tensor], i: int, positions, sz) -> torch.Tensor:
+def block(x, t: Dict[str, torch.Tensor], i: int, positions, sz, forced=None, margins=None) -> torch.Tensor:
     """x += mixer(norm(x)); x += feed_forward(norm(x)) (models/llama/common/src/compute.rs:204-336)."""
     p = f"blk.{i}."
     x1 = rms_norm(x, t[p + "attn_norm.weight"], sz["eps"])
@@ -180,7 +194,7 @@ def block(x, t: Dict[str, torch.Tensor], i: int, positions, sz) -> torch.Tensor:
             t[p + "ffn_gate_inp.weight"],
             t[p + "ffn_gate_up_exps.weight"],
             t[p + "ffn_down_exps.weight"],
-            sz["nexp_use"],
+            sz["nexp_use"], forced, margins,
         )
     else:
         x = x + dense_feed_forward(x1, t[p + "ffn_gate_up.weight"], t[p + "ffn_down.weight"])
@@ -188,7 +202,7 @@ def block(x, t: Dict[str, torch.Tensor], i: int, positions, sz) -> torch.Tensor:
 
 
 def forward(cfg: dict, t: Dict[str, torch.Tensor], tokens: Sequence[int],
-            want: Optional[Sequence[int]] = None) -> torch.Tensor:
+            want: Optional[Sequence[int]] = None, forced_routes=None, margins_out=None) -> torch.Tensor:
     """Logits [len(want), vocab] of one whole sequence that starts at position 0; ``want`` defaults
     to every position.  Final norm and head only on the wanted rows
     (models/llama/common/src/compute.rs:343-365); a missing ``output.weight`` means the head is
@@ -197,7 +211,11 @@ def forward(cfg: dict, t: Dict[str, torch.Tensor], tokens: Sequence[int],
     positions = list(range(len(tokens)))
     x = embedding(t["token_embd.weight"], tokens)
     for i in range(sz["nblk"]):
-        x = block(x, t, i, positions, sz)
+        # forced_routes[i][a]: experts token a must use in layer i; margins_out[i]: see moe_feed_forward
+        m = [] if margins_out is not None else None
+        x = block(x, t, i, positions, sz, None if forced_routes is None else forced_routes[i], m)
+        if margins_out is not None:
+            margins_out.append(m)
     rows = list(range(len(tokens))) if want is None else list(want)
     x = rms_norm(x[rows], t["output_norm.weight"], sz["eps"])
     head = t.get("output.weight", t["token_embd.weight"])

@@ -6,9 +6,10 @@
 """
 from .api import load, parse_dtype, random_model, read_config, write_random_model
 from .config import ConfigError, LlamaMeta, register_architecture
-from .engine import Engine, StepError
+from .engine import Engine, StepError, generate, GenerationResult
+from .sampling import SampleArgs, SampleArgsError
 from .cache import CacheError
 from .weights import WeightError
 
-__all__ = ["load", "random_model", "write_random_model", "read_config", "parse_dtype", "Engine", "LlamaMeta",
+__all__ = ["load", "random_model", "write_random_model", "read_config", "parse_dtype", "Engine", "LlamaMeta", "generate", "GenerationResult", "SampleArgs", "SampleArgsError",
            "ConfigError", "WeightError", "CacheError", "StepError", "register_architecture"]

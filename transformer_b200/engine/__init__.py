@@ -1,2 +1,3 @@
 from .engine import Engine, StepError
 from .context import StepContext, Workspace
+from .generate import GenerationResult, Timing, generate, plan_batches, verdict

@@ -120,7 +120,7 @@ class StepContext:
         event.record()
         self._dev = dev
         self._offsets = offsets
-        self._ones = {}
+        self.run_index = -1     # which entry of the run order is executing
 
     def _view(self, name: str) -> torch.Tensor:
         o, n = self._offsets[name]
@@ -137,6 +137,13 @@ class StepContext:
     def page_table(self, cache_view=None) -> torch.Tensor:
         """[B, max_pages] pages of each sequence, for the storage kind of ``cache_view``."""
         return self._view("page_table")
+
+    def record(self, name: str, tensor: torch.Tensor) -> None:
+        """Hand a copy of an intermediate result to the engine's recorder, if one is set (a debugging
+        aid: which experts were chosen, what a part produced).  Costs nothing when none is set."""
+        rec = self.engine.recorder
+        if rec is not None:
+            rec(name, self.run_index, tensor.detach().clone())
 
     def scratch(self, name: str, shape, dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)

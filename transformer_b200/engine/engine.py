@@ -53,6 +53,7 @@ class Engine:
                            max_slots=max_slots, dtype=dtype, device=device)
         self.workspace = Workspace(device)
         self._identity_tables = {}
+        self.recorder = None    # callable(name, run index, tensor copy) for debugging; see StepContext.record
         self._tile_sizes = sorted({lib.attention_tile_tokens(m.nh, m.nkvh) for m in mixers
                                    if hasattr(m, "nh") and hasattr(m, "nkvh")})
         self._staging = []
@@ -187,6 +188,7 @@ class Engine:
         pending = None
         for r, entry in enumerate(self.spec.order):
             layer = self.layers[entry.layer]
+            ctx.run_index = r
             pending = layer.forward(ctx, x, pending, self.cache.view(r), self.cache.state_of(r))
         n_out = len(ctx.h_want)
         logits = logits_out if logits_out is not None else \

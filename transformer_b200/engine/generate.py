@@ -1,0 +1,161 @@
+"""The generation loop above the step function.
+
+The reference's loop serves one sequence: the whole prompt in the first call, then one token per
+call, until the end token is sampled (it is neither kept nor fed back) or ``max_steps`` calls are
+made; it then prints a table total / prefill / decode with tokens, time and time per token
+(test-utils/src/lib.rs:128-203).  This loop does the same for many requests: it cuts them into
+batches that fit the cache, runs each batch's prompts (of unequal lengths) in one step and then
+one token per live sequence per step, lets sequences that end leave the batch, gives the batch's
+slots back when it ends, and goes on with the next batch.
+
+The decisions (which requests form a batch, which sequences go on) are plain functions of
+integers, so they can be tested without a device; the model is reached through three callables.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..cache.slots import PAGE
+from ..sampling.args import SampleArgs, uniform
+
+
+@dataclass
+class Timing:
+    prefill_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_tokens: int = 0
+    decode_seconds: float = 0.0
+
+    def table(self) -> str:
+        """The reference's table (test-utils/src/lib.rs:175-202) plus tokens per second."""
+        rows = [("total", self.prefill_tokens + self.decode_tokens, self.prefill_seconds + self.decode_seconds),
+                ("prefill", self.prefill_tokens, self.prefill_seconds),
+                ("decode", self.decode_tokens, self.decode_seconds)]
+        out = [f"{'':>8} | {'num tokens':>10} | {'elapse':>10} | {'time per token':>14} | {'tokens/s':>10}"]
+        for name, n, s in rows:
+            per = f"{s / n * 1e3:.3f}ms" if n else "-"
+            rate = f"{n / s:.1f}" if s > 0 else "-"
+            out.append(f"{name:>8} | {n:>10} | {s * 1e3:>8.3f}ms | {per:>14} | {rate:>10}")
+        return "\n".join(out)
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[List[int]]            # generated tokens per request, the stop token not included
+    finished: List[str]                # "stop" | "length" | "context" per request
+    timing: Timing = field(default_factory=Timing)
+    batches: List[List[int]] = field(default_factory=list)
+
+
+def plan_batches(prompt_lens: Sequence[int], max_new: Sequence[int], *, max_batch: int, n_pages: int,
+                 max_context: int) -> List[List[int]]:
+    """Requests in their order, cut into batches: at most max_batch sequences, and pages enough for
+    every sequence of a batch to reach its longest possible length."""
+    batches, cur, cur_pages = [], [], 0
+    for i, (n, m) in enumerate(zip(prompt_lens, max_new)):
+        if n <= 0:
+            raise ValueError(f"request {i} has an empty prompt")
+        if n > max_context:
+            raise ValueError(f"request {i}: a prompt of {n} tokens exceeds the context of {max_context}")
+        reach = min(n + max(m, 0), max_context)
+        pages = (reach + PAGE - 1) // PAGE
+        if pages > n_pages:
+            raise ValueError(f"request {i} needs {pages} cache pages of {PAGE} tokens; the cache has {n_pages}")
+        if cur and (len(cur) >= max_batch or cur_pages + pages > n_pages):
+            batches.append(cur)
+            cur, cur_pages = [], 0
+        cur.append(i)
+        cur_pages += pages
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def verdict(token: int, n_generated_before: int, length_before: int, *, stop_tokens, max_new: int,
+            max_context: int):
+    """What happens to a sequence that has just sampled ``token``: (keep the token?, why it ends or
+    None).  length_before counts prompt + generated tokens already in the cache."""
+    if token in stop_tokens:
+        return False, "stop"                       # test-utils/src/lib.rs:166-168
+    if n_generated_before + 1 >= max_new:
+        return True, "length"
+    if length_before + 1 > max_context:
+        return True, "context"                     # no room to feed this token back
+    return True, None
+
+
+def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[int] = None,
+             sample_args: SampleArgs = SampleArgs(), stop_tokens: Optional[Sequence[int]] = None,
+             seed: int = 0, max_batch: Optional[int] = None, on_token: Optional[Callable] = None
+             ) -> GenerationResult:
+    """Token ids in, token ids out.
+
+    max_steps: most tokens generated per request (the reference's MAX_STEPS counts model calls,
+    each of which yields one token; default: until the context is full).  stop_tokens default to
+    the ones the model's configuration declares.  ``seed`` fixes the sampler per request."""
+    import torch
+    from ..sampling.sampler import Sampler
+
+    spec = engine.spec
+    stops = frozenset(spec.stop_tokens if stop_tokens is None else stop_tokens)
+    n_req = len(prompts)
+    limit = [spec.max_context - len(p) + 1 if max_steps is None else int(max_steps) for p in prompts]
+    if any(m <= 0 for m in limit) and max_steps is not None:
+        return GenerationResult([[] for _ in prompts], ["length"] * n_req)
+    table = engine.cache.table
+    if max_batch is None:
+        max_batch = table.max_slots
+    max_batch = min(max_batch, table.max_slots - table.slots.held)
+    batches = plan_batches([len(p) for p in prompts], limit, max_batch=max_batch,
+                           n_pages=table.pages.free, max_context=spec.max_context)
+    sampler = getattr(engine, "_sampler", None)
+    if sampler is None:
+        sampler = engine._sampler = Sampler(engine.device)
+    out: List[List[int]] = [[] for _ in prompts]
+    why: List[Optional[str]] = [None] * n_req
+    timing = Timing()
+
+    def run_step(reqs, slots, toks):
+        logits = engine.step(slots, toks)
+        u = None if sample_args.greedy else [uniform(seed, r, len(out[r])) for r in reqs]
+        ids, _ = sampler.sample(logits, sample_args, u)
+        return ids.cpu().tolist()    # the one device-to-host read of the step (infer.rs:140-146)
+
+    for batch in batches:
+        slots = {r: engine.open() for r in batch}
+        try:
+            live = list(batch)
+            feed = {r: list(prompts[r]) for r in batch}
+            first = True
+            while live:
+                torch.cuda.synchronize(engine.device)
+                t0 = time.perf_counter()
+                ids = run_step(live, [slots[r] for r in live], [feed[r] for r in live])
+                dt = time.perf_counter() - t0
+                if first:
+                    timing.prefill_tokens += sum(len(feed[r]) for r in live)
+                    timing.prefill_seconds += dt
+                    first = False
+                else:
+                    timing.decode_tokens += len(live)
+                    timing.decode_seconds += dt
+                nxt = []
+                for r, tok in zip(live, ids):
+                    keep, end = verdict(tok, len(out[r]), engine.cache.length(slots[r]), stop_tokens=stops,
+                                        max_new=limit[r], max_context=spec.max_context)
+                    if keep:
+                        out[r].append(tok)
+                        if on_token is not None:
+                            on_token(r, tok)
+                    if end is None:
+                        feed[r] = [tok]
+                        nxt.append(r)
+                    else:
+                        why[r] = end
+                live = nxt
+        finally:
+            for s in slots.values():
+                engine.close(s)
+    return GenerationResult(out, [w or "length" for w in why], timing, batches)

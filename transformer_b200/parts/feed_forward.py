@@ -73,6 +73,7 @@ class MoE(FeedForward):
         M = nt * self.k
         sfx = lib.suffix(self.dtype)
         idx, w = self.route(ctx, x1)
+        ctx.record("moe.topk_idx", idx)
         offsets = ctx.scratch("moe.offsets", (self.E + 1,), torch.int32)
         sorted_token = ctx.scratch("moe.sorted_token", (M,), torch.int32)
         pair_row = ctx.scratch("moe.pair_row", (M,), torch.int32)

@@ -1,0 +1,2 @@
+from .args import SampleArgs, SampleArgsError, uniform
+from .sampler import Sampler
