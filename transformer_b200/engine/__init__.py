@@ -1,3 +1,3 @@
 from .engine import Engine, StepError
 from .context import StepContext, Workspace
-from .generate import GenerationResult, Timing, generate, plan_batches, verdict
+from .generate import GenerationResult, Timing, generate, plan_batches, run_batches, verdict

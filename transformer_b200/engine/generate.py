@@ -86,6 +86,53 @@ def verdict(token: int, n_generated_before: int, length_before: int, *, stop_tok
     return True, None
 
 
+def run_batches(batches, prompts, limit, stops, max_context, *, open_slot, close_slot, length_of,
+                step_and_sample, clock=time.perf_counter, on_token=None):
+    """The loop itself, reached only through callables so that it runs without a device:
+    open_slot() -> slot, close_slot(slot), length_of(slot) -> tokens in the cache,
+    step_and_sample(requests, slots, token lists, tokens generated so far per request) -> one new
+    token per request, clock() -> seconds (the real one waits for the device first)."""
+    out: List[List[int]] = [[] for _ in prompts]
+    why: List[Optional[str]] = [None] * len(prompts)
+    timing = Timing()
+    for batch in batches:
+        slots = {r: open_slot() for r in batch}
+        try:
+            live = list(batch)
+            feed = {r: list(prompts[r]) for r in batch}
+            first = True
+            while live:
+                t0 = clock()
+                ids = step_and_sample(live, [slots[r] for r in live], [feed[r] for r in live],
+                                      [len(out[r]) for r in live])
+                dt = clock() - t0
+                if first:
+                    timing.prefill_tokens += sum(len(feed[r]) for r in live)
+                    timing.prefill_seconds += dt
+                    first = False
+                else:
+                    timing.decode_tokens += len(live)
+                    timing.decode_seconds += dt
+                nxt = []
+                for r, tok in zip(live, ids):
+                    keep, end = verdict(tok, len(out[r]), length_of(slots[r]), stop_tokens=stops,
+                                        max_new=limit[r], max_context=max_context)
+                    if keep:
+                        out[r].append(tok)
+                        if on_token is not None:
+                            on_token(r, tok)
+                    if end is None:
+                        feed[r] = [tok]
+                        nxt.append(r)
+                    else:
+                        why[r] = end
+                live = nxt
+        finally:
+            for s in slots.values():   # the batch has ended: what it held is used again
+                close_slot(s)
+    return out, [w or "length" for w in why], timing
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[int] = None,
              sample_args: SampleArgs = SampleArgs(), stop_tokens: Optional[Sequence[int]] = None,
              seed: int = 0, max_batch: Optional[int] = None, on_token: Optional[Callable] = None
@@ -101,9 +148,9 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[in
     spec = engine.spec
     stops = frozenset(spec.stop_tokens if stop_tokens is None else stop_tokens)
     n_req = len(prompts)
-    limit = [spec.max_context - len(p) + 1 if max_steps is None else int(max_steps) for p in prompts]
-    if any(m <= 0 for m in limit) and max_steps is not None:
+    if max_steps is not None and max_steps <= 0:
         return GenerationResult([[] for _ in prompts], ["length"] * n_req)
+    limit = [spec.max_context - len(p) + 1 if max_steps is None else int(max_steps) for p in prompts]
     table = engine.cache.table
     if max_batch is None:
         max_batch = table.max_slots
@@ -113,49 +160,18 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[in
     sampler = getattr(engine, "_sampler", None)
     if sampler is None:
         sampler = engine._sampler = Sampler(engine.device)
-    out: List[List[int]] = [[] for _ in prompts]
-    why: List[Optional[str]] = [None] * n_req
-    timing = Timing()
 
-    def run_step(reqs, slots, toks):
+    def step_and_sample(reqs, slots, toks, n_generated):
         logits = engine.step(slots, toks)
-        u = None if sample_args.greedy else [uniform(seed, r, len(out[r])) for r in reqs]
+        u = None if sample_args.greedy else [uniform(seed, r, n) for r, n in zip(reqs, n_generated)]
         ids, _ = sampler.sample(logits, sample_args, u)
         return ids.cpu().tolist()    # the one device-to-host read of the step (infer.rs:140-146)
 
-    for batch in batches:
-        slots = {r: engine.open() for r in batch}
-        try:
-            live = list(batch)
-            feed = {r: list(prompts[r]) for r in batch}
-            first = True
-            while live:
-                torch.cuda.synchronize(engine.device)
-                t0 = time.perf_counter()
-                ids = run_step(live, [slots[r] for r in live], [feed[r] for r in live])
-                dt = time.perf_counter() - t0
-                if first:
-                    timing.prefill_tokens += sum(len(feed[r]) for r in live)
-                    timing.prefill_seconds += dt
-                    first = False
-                else:
-                    timing.decode_tokens += len(live)
-                    timing.decode_seconds += dt
-                nxt = []
-                for r, tok in zip(live, ids):
-                    keep, end = verdict(tok, len(out[r]), engine.cache.length(slots[r]), stop_tokens=stops,
-                                        max_new=limit[r], max_context=spec.max_context)
-                    if keep:
-                        out[r].append(tok)
-                        if on_token is not None:
-                            on_token(r, tok)
-                    if end is None:
-                        feed[r] = [tok]
-                        nxt.append(r)
-                    else:
-                        why[r] = end
-                live = nxt
-        finally:
-            for s in slots.values():
-                engine.close(s)
-    return GenerationResult(out, [w or "length" for w in why], timing, batches)
+    def clock():
+        torch.cuda.synchronize(engine.device)
+        return time.perf_counter()
+
+    out, why, timing = run_batches(batches, prompts, limit, stops, spec.max_context, open_slot=engine.open,
+                                   close_slot=engine.close, length_of=engine.cache.length,
+                                   step_and_sample=step_and_sample, clock=clock, on_token=on_token)
+    return GenerationResult(out, why, timing, batches)
