@@ -56,7 +56,7 @@ class FakeEngine:
 
 def _generate(eng, prompts, max_steps, stop_tokens=(0,)):
     from transformer_b200.engine import run_batches
-    limit = [eng.max_context - len(p) + 1 if max_steps is None else max_steps for p in prompts]
+    limit = [1 << 60 if max_steps is None else max_steps for _ in prompts]
     batches = plan_batches([len(p) for p in prompts], limit, max_batch=eng.table.max_slots,
                            n_pages=eng.table.pages.free, max_context=eng.max_context)
     out, why, timing = run_batches(batches, prompts, limit, frozenset(stop_tokens), eng.max_context,

@@ -150,7 +150,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[in
     n_req = len(prompts)
     if max_steps is not None and max_steps <= 0:
         return GenerationResult([[] for _ in prompts], ["length"] * n_req)
-    limit = [spec.max_context - len(p) + 1 if max_steps is None else int(max_steps) for p in prompts]
+    limit = [1 << 60 if max_steps is None else int(max_steps) for _ in prompts]   # None: the context ends it
     table = engine.cache.table
     if max_batch is None:
         max_batch = table.max_slots
