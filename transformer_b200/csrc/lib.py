@@ -78,8 +78,13 @@ def _error_text(code: int) -> str:
     return f"CUDA error {code}"
 
 
+launch_count = 0     # launchers called so far (a launcher may start more than one kernel)
+
+
 def call(name: str, *args) -> None:
     """Launch ``name`` on torch's current stream."""
+    global launch_count
+    launch_count += 1
     fn = getattr(library(), name)
     rc = fn(*args, torch.cuda.current_stream().cuda_stream)
     if rc != 0:

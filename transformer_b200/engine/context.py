@@ -34,10 +34,11 @@ class AttentionTiles:
 class Workspace:
     """Named scratch buffers, kept between steps and grown when a step needs more."""
 
-    def __init__(self, device):
+    def __init__(self, device, on_grow=None):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
-        self.frozen = False   # set while a CUDA graph that uses these buffers is alive or captured
+        self.frozen = False     # set while a CUDA graph is being captured
+        self.on_grow = on_grow  # called before a buffer is replaced (whoever kept its address must forget it)
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -47,7 +48,9 @@ class Workspace:
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
             if self.frozen:
-                raise RuntimeError(f"scratch buffer {name!r} would grow after CUDA graphs captured it")
+                raise RuntimeError(f"scratch buffer {name!r} would grow while a CUDA graph is captured")
+            if buf is not None and self.on_grow is not None:
+                self.on_grow()
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:n].view(*shape)
@@ -117,6 +120,7 @@ class StepContext:
             o, n = offsets[k]
             hv[o:o + n] = v
         dev[:total].copy_(host[:total], non_blocking=True)
+        engine.last_h2d_bytes = total * 4
         event.record()
         self._dev = dev
         self._offsets = offsets

@@ -51,7 +51,7 @@ class Engine:
         self.cache = Cache([m.cache_need() for m in mixers], [m.state_need() for m in mixers],
                            [e.cache_of for e in runs], max_tokens=max_tokens, max_context=spec.max_context,
                            max_slots=max_slots, dtype=dtype, device=device)
-        self.workspace = Workspace(device)
+        self.workspace = Workspace(device, on_grow=self._drop_graphs)
         self._identity_tables = {}
         self.recorder = None    # callable(name, run index, tensor copy) for debugging; see StepContext.record
         self._tile_sizes = sorted({lib.attention_tile_tokens(m.nh, m.nkvh) for m in mixers
@@ -59,6 +59,11 @@ class Engine:
         self._staging = []
         self._staging_next = 0
         self._staging_dev = None
+        # decode steps (one token per sequence) replay a CUDA graph captured per batch size
+        self.use_graphs = True
+        self.graph_max_batch = 256
+        self._graphs = {}        # batch size -> (graph, static logits)
+        self._graph_seen = {}    # batch size -> decode steps run eagerly so far
 
     # ---- construction ---------------------------------------------------------------------
     def _bind(self, weights) -> None:
@@ -73,11 +78,19 @@ class Engine:
                 part.bind({n: weights[("layers", i, pname, n)] for n in part.parameters()})
         self.final_norm.bind({n: weights[("final_norm", n)] for n in self.final_norm.parameters()})
 
+    def _drop_graphs(self) -> None:
+        """Captured graphs hold raw addresses of scratch and staging memory; when either moves, they go."""
+        if self._graphs:
+            torch.cuda.synchronize(self.device)
+        self._graphs.clear()
+        self._graph_seen.clear()
+
     def staging(self, n_ints: int):
         """A pinned host buffer, the device buffer it is copied to, and the event of its last copy."""
-        size = max(4096, 1 << (int(n_ints) - 1).bit_length())
+        size = max(1 << 16, 1 << (int(n_ints) - 1).bit_length())
         if not self._staging or self._staging[0][0].numel() < size:
             torch.cuda.synchronize(self.device)
+            self._drop_graphs()           # captured graphs read the old device buffer
             self._staging = [(torch.empty(size, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
                              for _ in range(4)]
             self._staging_dev = torch.empty(size, dtype=torch.int32, device=self.device)
@@ -96,12 +109,17 @@ class Engine:
 
     # ---- the step ---------------------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+             want: Optional[Sequence[Sequence[int]]] = None, *, device_tokens: Optional[torch.Tensor] = None
+             ) -> torch.Tensor:
         """Run the given next tokens of the given sequences as one batch, from the cache.
 
         slots[b]: an open slot; tokens[b]: its next tokens (one or many, lengths may differ);
         want[b]: indices into tokens[b] whose logits are wanted (default: the last).  Returns float
         logits [sum of len(want[b]), vocab] on the device, in the order of the batch and of ``want``.
+
+        device_tokens: for one-token steps, an int32 device tensor [B] that holds the tokens (for
+        instance what the sampler just wrote); ``tokens`` then only gives the shape.  Nothing comes
+        back to the host between such steps.
         """
         B = len(slots)
         if len(tokens) != B:
@@ -133,6 +151,11 @@ class Engine:
         pos0 = [self.cache.extend(s, len(t)) for s, t in zip(slots, tokens)]
 
         n_total = sum(len(t) for t in tokens)
+        if n_total == B and all(list(w) == [0] for w in want) and \
+                (device_tokens is not None or (self.use_graphs and B <= self.graph_max_batch)):
+            return self._run_decode(slots, tokens, pos0, device_tokens)
+        if device_tokens is not None:
+            raise StepError("device_tokens serve steps of one token per sequence that want its logits")
         if n_total <= self.max_step_tokens:
             rows, base = [], 0
             for b in range(B):
@@ -175,6 +198,41 @@ class Engine:
             if p_dest:
                 out[torch.tensor(p_dest, device=self.device)] = logits
         return out
+
+    def _run_decode(self, slots, tokens, pos0, device_tokens=None) -> torch.Tensor:
+        """One token for each of B sequences.  The first such step of a batch size runs eagerly
+        (it also sizes the scratch memory), the second is captured into a CUDA graph, and from then
+        on the step is: copy the step's index arrays, replay.  The arrays have the same layout at
+        every step of a batch size (the page table has its full width), so the graph stays valid."""
+        B = len(slots)
+        fixed = self.cache.table.max_pages_per_seq
+        ctx = StepContext(self, slots, tokens, pos0, list(range(B)), self._tile_sizes, fixed_pages=fixed)
+        if device_tokens is not None:
+            ctx.tok_ids.copy_(device_tokens.view(-1)[:B])
+        if not self.use_graphs or B > self.graph_max_batch:
+            return self._forward(ctx)
+        entry = self._graphs.get(B)
+        if entry is None:
+            seen = self._graph_seen.get(B, 0)
+            self._graph_seen[B] = seen + 1
+            if seen == 0:
+                return self._forward(ctx)
+            logits = torch.empty((B, self.spec.vocab), dtype=torch.float32, device=self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = lib.launch_count
+            self.workspace.frozen = True      # scratch must not move while it is being captured
+            try:
+                with torch.cuda.graph(graph):
+                    self._forward(ctx, logits)
+            finally:
+                self.workspace.frozen = False
+            entry = (graph, logits, lib.launch_count - before)
+            lib.launch_count = before
+            self._graphs[B] = entry
+        graph, logits, nodes = entry
+        graph.replay()
+        lib.launch_count += nodes             # a replay launches every captured kernel again
+        return logits
 
     def _run(self, slots, tokens, pos0, rows, *, fixed_pages=None, logits_out=None) -> torch.Tensor:
         ctx = StepContext(self, slots, tokens, pos0, rows, self._tile_sizes, fixed_pages=fixed_pages)
