@@ -1,0 +1,319 @@
+"""Each CUDA kernel alone against a plain float64/float32 restatement of the same operation, at
+sizes other than the tiny models' (odd widths, tails, head sizes in steps of 16, many groups)."""
+import math
+
+import pytest
+import torch
+
+from kernel_inputs import attention_case
+from plain import llama_moe_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _lib():
+    from transformer_b200.csrc import lib
+    return lib
+
+
+def _tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 2.0 ** -7) * scale
+
+
+def _rand(shape, dtype, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype).cuda()
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    lib = _lib()
+    V, d = 301, 72
+    table = _rand((V, d), dtype, 0)
+    tok = torch.tensor([5, 300, 0, 5, 17], dtype=torch.int32, device="cuda")
+    x = torch.empty((5, d), dtype=torch.float32, device="cuda")
+    lib.call("tb_embed_" + lib.suffix(dtype), tok.data_ptr(), table.data_ptr(), x.data_ptr(), 5, d)
+    assert torch.equal(x, table[tok.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [72, 4100])
+def test_add_rmsnorm(dtype, d):
+    lib = _lib()
+    n, eps = 7, 3e-6
+    x = _rand((n, d), torch.float32, 1, 2.0)
+    delta = _rand((n, d), dtype, 2)
+    w = _rand((d,), torch.float32, 3)
+    y = torch.empty((n, d), dtype=dtype, device="cuda")
+    x_in = x.clone()
+    lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), delta.data_ptr(), 0, w.data_ptr(), eps,
+             y.data_ptr(), n, d)
+    v = x_in.double() + delta.double()
+    assert torch.allclose(x.double(), v, atol=1e-6), "the stream is updated in place with a float sum"
+    ref = P.rms_norm(v.cpu(), w.double().cpu(), eps)
+    assert float((y.double().cpu() - ref).abs().max()) <= _tol(dtype, float(ref.abs().max()))
+    # gathered rows, no delta, no write-back
+    rows = torch.tensor([6, 0, 6], dtype=torch.int32, device="cuda")
+    y2 = torch.empty((3, d), dtype=dtype, device="cuda")
+    before = x.clone()
+    lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), 0, rows.data_ptr(), w.data_ptr(), eps,
+             y2.data_ptr(), 3, d)
+    assert torch.equal(x, before)
+    ref2 = P.rms_norm(before[rows.long()].double().cpu(), w.double().cpu(), eps)
+    assert float((y2.double().cpu() - ref2).abs().max()) <= _tol(dtype, float(ref2.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pairing", ["adjacent", "half"])
+def test_rope_and_cache_write(dtype, pairing):
+    lib = _lib()
+    nh, nkvh, dh, theta, nctx = 5, 1, 48, 12345.0, 300
+    pos = [0, 1, 63, 64, 200, 299]
+    seqs = [0, 1, 1, 1, 0, 1]
+    nt = len(pos)
+    qkv = _rand((nt, (nh + 2 * nkvh) * dh), dtype, 4)
+    orig = qkv.clone()
+    i = torch.arange(dh // 2, dtype=torch.float64)
+    ang = torch.arange(nctx, dtype=torch.float64)[:, None] * theta ** (-2.0 * i / dh)[None]
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    n_pages, max_pages = 12, 5
+    table = torch.tensor([[3, 7, 1, 9, 11], [2, 8, 0, 4, 10]], dtype=torch.int32, device="cuda")
+    kc = torch.zeros((n_pages, nkvh, 64, dh), dtype=dtype, device="cuda")
+    vc = torch.zeros_like(kc)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    seq_t, pos_t = i32(seqs), i32(pos)      # kept alive: a temporary's memory would be handed out again
+    lib.call("tb_rope_cache_" + lib.suffix(dtype), qkv.data_ptr(), seq_t.data_ptr(), pos_t.data_ptr(),
+             table.data_ptr(), max_pages, cos.data_ptr(), sin.data_ptr(), kc.data_ptr(), vc.data_ptr(), nt, nh,
+             nkvh, dh, 1 if pairing == "half" else 0)
+    o = orig.double().cpu().reshape(nt, nh + 2 * nkvh, dh)
+    q_ref = P.rope(o[:, :nh], pos, theta, pairing)
+    k_ref = P.rope(o[:, nh:nh + nkvh], pos, theta, pairing)
+    got = qkv.double().cpu().reshape(nt, nh + 2 * nkvh, dh)
+    tol = _tol(dtype, 4.0)
+    assert float((got[:, :nh] - q_ref).abs().max()) <= tol
+    for a in range(nt):
+        page = int(table[seqs[a], pos[a] // 64])
+        assert float((kc[page, :, pos[a] % 64].double().cpu() - k_ref[a]).abs().max()) <= tol
+        assert torch.equal(vc[page, :, pos[a] % 64].cpu(), orig.cpu().reshape(nt, -1, dh)[a, nh + nkvh:])
+    assert int((kc.abs().sum(dim=(1, 3)) > 0).sum()) == nt, "nothing else in the cache was touched"
+
+
+# ---------------------------------------------------------------------------------------------
+def _run_attention(lib, c, dtype, splits, decode):
+    nt, nh, dh = c["nt"], c["nh"], c["dh"]
+    out = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
+    partial = torch.empty(max(1, nt * nh * splits * (dh + 2)), dtype=torch.float32, device="cuda")
+    scale = 1.0 / math.sqrt(dh)
+    if decode:
+        seq = torch.repeat_interleave(c["tile_seq"], c["tile_nq"])
+        ok = lib.try_call("tb_attention_decode_" + lib.suffix(dtype), c["q"].data_ptr(), out.data_ptr(),
+                          c["kc"].data_ptr(), c["vc"].data_ptr(), seq.data_ptr(), c["tok_pos"].data_ptr(),
+                          c["table"].data_ptr(), partial.data_ptr(), nt, c["max_pages"], nh * dh, nh, c["nkvh"], dh,
+                          splits, scale)
+        if not ok:
+            return None
+    else:
+        lib.call("tb_attention_" + lib.suffix(dtype), c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
+                 c["vc"].data_ptr(), c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(), c["tile_nq"].data_ptr(),
+                 c["tok_pos"].data_ptr(), c["table"].data_ptr(), partial.data_ptr(), c["tiles"], nt, c["max_pages"],
+                 nh * dh, nh, c["nkvh"], dh, splits, scale)
+    return out.double().cpu().reshape(nt, nh, dh)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 16), (3, 1, 48), (6, 6, 80), (40, 2, 32), (2, 1, 256), (8, 8, 128)])
+def test_attention_general(dtype, nh, nkvh, dh):
+    lib = _lib()
+    tq = lib.attention_tile_tokens(nh, nkvh)
+    # prompts from zero, a continued prompt, single tokens: all in one ragged batch
+    c = attention_case([37, 1, 9, 1, 70], [0, 130, 64, 0, 31], nh, nkvh, dh, dtype, tq, seed=nh + dh)
+    for splits in (1, 3):
+        got = _run_attention(lib, c, dtype, splits, decode=False)
+        assert float((got - c["ref"]).abs().max()) <= _tol(dtype, 4.0), f"splits {splits}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 16), (3, 1, 32), (8, 8, 128), (12, 2, 64), (20, 2, 128), (2, 1, 256)])
+def test_attention_decode(dtype, nh, nkvh, dh):
+    lib = _lib()
+    c = attention_case([1, 1, 1, 1, 1], [0, 63, 64, 700, 129], nh, nkvh, dh, dtype, 1, seed=3 * nh + dh)
+    for splits in (1, 2, 7):
+        got = _run_attention(lib, c, dtype, splits, decode=True)
+        if got is None:
+            assert dtype == torch.float32 and dh == 256, "only a float head of 256 is refused here"
+            return
+        assert float((got - c["ref"]).abs().max()) <= _tol(dtype, 4.0), f"splits {splits}"
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_attention_finds_one_far_key(decode):
+    """Among hundreds of keys one, far back and on an early page, is made to dominate: the output
+    must be its value.  Shows a wrong page, a dropped key slice, a wrong mask."""
+    lib = _lib()
+    nh, nkvh, dh = 4, 2, 64
+    for far in (0, 5, 64, 391):
+        c = attention_case([1], [900], nh, nkvh, dh, torch.float32, 1, seed=far, scale_key=(0, far, 40.0))
+        # the query that points at that key: q = k_far (already scaled), so its score towers
+        kfar_page = int(c["table"][0, far // 64])
+        kfar = c["kc"][kfar_page, :, far % 64]                    # [nkvh, dh]
+        c["q"] = kfar.repeat_interleave(nh // nkvh, dim=0).reshape(1, nh * dh).contiguous() * 0.05
+        vfar = c["vc"][kfar_page, :, far % 64].double().cpu()
+        for splits in (1, 4):
+            got = _run_attention(lib, c, torch.float32, splits, decode)
+            for h in range(nh):
+                assert float((got[0, h] - vfar[h // 2]).abs().max()) < 1e-3, f"far key {far}, splits {splits}"
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 16, 8), (5, 50, 24), (70, 129, 100), (3, 688, 4096), (130, 64, 688)])
+def test_gemm_simt_dense(dtype, M, N, K):
+    from transformer_b200.parts.linear import gemm_simt
+    a, w = _rand((M, K), dtype, 5), _rand((N, K), dtype, 6, 0.1)
+    ref = a.double() @ w.double().T
+    for out_dtype, kind in ((dtype, 0), (torch.float32, 1)):
+        out = torch.empty((M, N), dtype=out_dtype, device="cuda")
+        gemm_simt(a, w, out, out_kind=kind)
+        assert float((out.double() - ref).abs().max()) <= _tol(out_dtype, float(ref.abs().max()))
+
+
+def _grouped_case(dtype, E, k, nt, d, di, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = _rand((nt, d), dtype, seed + 1)
+    wgu = _rand((E, 2 * di, d), dtype, seed + 2, 0.1)
+    wd = _rand((E, d, di), dtype, seed + 3, 0.1)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(nt)]).to(torch.int32).cuda()
+    return x, wgu, wd, idx
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("E,k,nt,d,di", [(4, 2, 9, 64, 40), (16, 4, 8, 256, 86), (6, 3, 200, 96, 80), (3, 3, 1, 72, 16)])
+def test_dispatch_grouped_products_and_combine(dtype, E, k, nt, d, di):
+    """token -> expert dispatch, the grouped gate/up product with swiglu, the grouped down product
+    and the weighted combine, against a per-token loop."""
+    lib = _lib()
+    from transformer_b200.parts.linear import grouped_matmul, gemm_simt
+    x, wgu, wd, idx = _grouped_case(dtype, E, k, nt, d, di, seed=E + nt)
+    w = torch.softmax(_rand((nt, k), torch.float32, 9), dim=1).contiguous()
+    M = nt * k
+    off = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    st = torch.empty(M, dtype=torch.int32, device="cuda")
+    pr = torch.empty(M, dtype=torch.int32, device="cuda")
+    lib.call("tb_moe_dispatch", idx.data_ptr(), off.data_ptr(), st.data_ptr(), pr.data_ptr(), M, k, E)
+    offc, stc, prc = off.cpu(), st.cpu(), pr.cpu()
+    assert offc[0] == 0 and offc[-1] == M and sorted(prc.tolist()) == list(range(M))
+    for p in range(M):
+        e = int(idx.view(-1)[p])
+        assert offc[e] <= prc[p] < offc[e + 1] and stc[prc[p]] == p // k
+    ref = torch.zeros(nt, d, dtype=torch.float64)
+    for t in range(nt):
+        for j in range(k):
+            e = int(idx[t, j])
+            ref[t] += float(w[t, j]) * P.expert_ffn(x[t].double().cpu(), wgu[e].double().cpu(), wd[e].double().cpu())
+    for use in ("auto", "simt"):
+        h = torch.empty((M, di), dtype=dtype, device="cuda")
+        y = torch.empty((M, d), dtype=dtype, device="cuda")
+        if use == "auto":
+            grouped_matmul(x, wgu, h, a_rows=st, group_offsets=off, groups=E, swiglu=True)
+            grouped_matmul(h, wd, y, group_offsets=off, groups=E)
+        else:
+            gemm_simt(x, wgu, h, a_rows=st, group_offsets=off, groups=E, out_kind=2)
+            gemm_simt(h, wd, y, group_offsets=off, groups=E, out_kind=0)
+        out = torch.empty((nt, d), dtype=dtype, device="cuda")
+        lib.call("tb_moe_combine_" + lib.suffix(dtype), y.data_ptr(), pr.data_ptr(), w.data_ptr(), out.data_ptr(),
+                 nt, d, k)
+        assert float((out.double().cpu() - ref).abs().max()) <= 2 * _tol(dtype, float(ref.abs().max())), use
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 8), (8, 50, 24), (9, 129, 104), (33, 688, 4096), (64, 4096, 688), (3, 1000, 72)])
+def test_gemm_skinny_dense(M, N, K):
+    from transformer_b200.parts.linear import gemm_skinny
+    a, w = _rand((M, K), torch.bfloat16, 7), _rand((N, K), torch.bfloat16, 8, 0.1)
+    ref = a.double() @ w.double().T
+    for out_dtype, kind in ((torch.bfloat16, 0), (torch.float32, 1)):
+        out = torch.empty((M, N), dtype=out_dtype, device="cuda")
+        assert gemm_skinny(a, w, out, out_kind=kind)
+        assert float((out.double() - ref).abs().max()) <= _tol(out_dtype, float(ref.abs().max()))
+    # a width that is no multiple of 8 is refused, not computed wrongly
+    a2, w2 = _rand((M, 20), torch.bfloat16, 7), _rand((N, 20), torch.bfloat16, 8)
+    assert not gemm_skinny(a2[:, :12].contiguous(), w2[:, :12].contiguous(),
+                           torch.empty((M, N), dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("E,k,d,nt", [(4, 2, 64, 5), (16, 4, 4096, 3), (6, 3, 100, 40), (70, 70, 24, 2), (33, 5, 72, 1100)])
+def test_router(dtype, E, k, d, nt):
+    lib = _lib()
+    x, wr = _rand((nt, d), dtype, 10), _rand((E, d), dtype, 11, 0.3)
+    idx = torch.empty((nt, k), dtype=torch.int32, device="cuda")
+    w = torch.empty((nt, k), dtype=torch.float32, device="cuda")
+    lg = torch.empty((nt, E), dtype=torch.float32, device="cuda")
+    lib.call("tb_router_" + lib.suffix(dtype), x.data_ptr(), wr.data_ptr(), idx.data_ptr(), w.data_ptr(),
+             lg.data_ptr(), nt, d, E, k)
+    ref_lg = x.double() @ wr.double().T
+    assert float((lg.double() - ref_lg).abs().max()) <= 2e-5 * max(1.0, float(ref_lg.abs().max())), \
+        "router logits are float whatever the storage type"
+    for t in range(0, nt, max(1, nt // 50)):
+        experts, weights = P.route(lg[t].double().cpu(), k)     # from the kernel's own logits: exact rule
+        assert idx[t].tolist() == experts
+        assert float((w[t].double().cpu() - weights).abs().max()) < 1e-5
+
+
+def test_router_ties_go_to_the_lower_expert():
+    lib = _lib()
+    E, k, d = 8, 3, 16
+    x = torch.ones((1, d), dtype=torch.float32, device="cuda")
+    wr = torch.zeros((E, d), dtype=torch.float32, device="cuda")
+    wr[[1, 4, 6, 7]] = 0.5                                  # four equal best logits
+    idx = torch.empty((1, k), dtype=torch.int32, device="cuda")
+    w = torch.empty((1, k), dtype=torch.float32, device="cuda")
+    lib.call("tb_router_f32", x.data_ptr(), wr.data_ptr(), idx.data_ptr(), w.data_ptr(), 0, 1, d, E, k)
+    assert idx[0].tolist() == [1, 4, 6] and torch.allclose(w, torch.full_like(w, 1 / 3))
+
+
+# ---------------------------------------------------------------------------------------------
+def _sample(lib, logits, u, t, k, p):
+    rows = logits.shape[0]
+    idx = torch.empty(rows, dtype=torch.int32, device="cuda")
+    val = torch.empty(rows, dtype=torch.float32, device="cuda")
+    uu = torch.tensor(u, dtype=torch.float32, device="cuda")
+    lib.call("tb_sample", logits.data_ptr(), logits.stride(0), uu.data_ptr(), rows, logits.shape[1], float(t), int(k),
+             float(p), idx.data_ptr(), val.data_ptr())
+    return idx.cpu().tolist(), val.cpu()
+
+
+@pytest.mark.parametrize("V", [5, 384, 32000, 50257])
+def test_sampling_argmax_and_ties(V):
+    lib = _lib()
+    lg = _rand((3, V), torch.float32, 12)
+    lg[1, [V // 2, V - 1]] = 50.0      # two equal maxima: the lower id wins
+    lg[2, 0] = 60.0
+    ids, vals = _sample(lib, lg, [0.5] * 3, 0.0, 0, 1.0)
+    assert ids == [int(torch.argmax(lg[0])), V // 2, 0]
+    assert torch.equal(vals, lg.cpu()[torch.arange(3), torch.tensor(ids)])
+    assert _sample(lib, lg, [0.9] * 3, 0.7, 1, 1.0)[0] == ids, "top_k = 1 is the argmax"
+
+
+@pytest.mark.parametrize("V,t,k,p", [(384, 0.8, 0, 1.0), (1000, 1.0, 40, 1.0), (1000, 1.3, 0, 0.9), (32000, 0.7, 50, 0.8),
+                                     (50, 1.0, 7, 0.5), (50, 2.0, 49, 0.999)])
+def test_sampling_draws_from_the_stated_distribution(V, t, k, p):
+    """For many uniform numbers the kernel's token must be the one whose interval of the cumulative
+    distribution (kept tokens in ascending id) holds u; a hair's breadth at an edge is allowed."""
+    lib = _lib()
+    rows = 64
+    lg = (_rand((1, V), torch.float32, 13) * 3).repeat(rows, 1).contiguous()
+    lg[0, 3] = lg[0, 11]          # equal logits inside the row
+    lg = lg[0:1].repeat(rows, 1).contiguous()
+    us = [(i + 0.37) / rows for i in range(rows)]
+    ids, _ = _sample(lib, lg, us, t, k, p)
+    kept, probs = P.sample_distribution(lg[0].cpu(), t, k, p)
+    cdf = [0.0]
+    for q in probs:
+        cdf.append(cdf[-1] + q)
+    for u, tok in zip(us, ids):
+        assert tok in kept, f"token {tok} is outside the kept set"
+        j = kept.index(tok)
+        assert cdf[j] - 1e-4 <= u <= cdf[j + 1] + 1e-4, f"u = {u}: token {tok} covers [{cdf[j]}, {cdf[j + 1]}]"

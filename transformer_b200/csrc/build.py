@@ -134,6 +134,11 @@ def ensure_built(verbose: bool = True) -> str:
         if r.returncode != 0:
             raise KernelBuildError(f"link failed:\n{r.stdout}")
         os.replace(tmp_lib, lib)   # atomic: a concurrent process sees the old state or the whole file
+        for o in objs:
+            try:
+                os.remove(o)
+            except OSError:
+                pass
     finally:
         done.set()
     if verbose:

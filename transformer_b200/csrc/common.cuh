@@ -71,4 +71,27 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// One 16-byte load as floats: 8 bfloat16 or 4 float values.
+template <typename T> struct Vec16;
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ __forceinline__ static void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 x = __bfloat1622float2(h[i]);
+            f[2 * i] = x.x;
+            f[2 * i + 1] = x.y;
+        }
+    }
+};
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    __device__ __forceinline__ static void load(const float* p, float (&f)[4]) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+};
+
 static inline int tb_last_error() { return (int)cudaGetLastError(); }

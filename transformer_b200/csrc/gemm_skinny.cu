@@ -1,0 +1,181 @@
+// Skinny (few-token) matrix products for decoding, bfloat16 on the tensor cores:
+//     Y[m, :] = X[row(m), :] . W[g(m)]^T        with a handful of rows m per weight matrix.
+//
+// A decode step multiplies a few activation rows with every weight it uses, so the step is bound
+// by reading the weights once from HBM.  The weight matrix is therefore the streamed operand:
+// it is the A operand (16 output columns x 16 k) of mma.sync.m16n8k16, loaded straight from
+// global memory with 16-byte loads, and the tokens are the n = 8 side.  Accumulation is float.
+//
+//  * grouped: W holds G matrices; rows of the problem are sorted by group (the experts of
+//    models/llama/common/src/compute.rs:319-330: every DISTINCT expert is read once per layer, not
+//    once per (token, expert) pair as in the reference's loop); G = 1 without offsets is dense.
+//  * x_rows gathers activation rows (token -> expert dispatch).
+//  * DUAL: W[g] is [2N, K]; gate = X.W[g][n], up = X.W[g][N + n]; stores silu(gate) * up
+//    (swiglu, compute.rs:324-326).
+//  * output bfloat16 or float (logits, router).
+//
+// One block = 16 output columns of one group.  Its 8 warps split K (warp w takes the 32-wide
+// k-steps w, w + 8, ...: neighbouring warps read neighbouring 64-byte pieces of a weight row) and
+// add their partial sums through shared memory.  Rows are taken 8 * NT at a time.
+//
+// The 8 values a thread loads per row with one 16-byte load are consecutive in k; the mma's
+// k-slots are fed in that order for both operands (a dot product does not care about the order of
+// its terms as long as both sides agree), so no shuffle or shared-memory transpose is needed.
+//
+// Sizes: K a multiple of 8 (16-byte loads), any N, any number of rows; others are refused.
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_COLS 16
+
+struct SkinnyArgs {
+    const __nv_bfloat16* X;
+    const int* x_rows;
+    const __nv_bfloat16* W;
+    void* Y;
+    const int* group_offsets;
+    long long w_group_stride;
+    int ldx, ldw, ldy;
+    int M, N, K, G;
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
+    return *reinterpret_cast<const uint4*>(p);
+}
+
+template <int NT, bool DUAL, typename TY>
+__global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const SkinnyArgs a) {
+    constexpr int ROWS = 8 * NT;
+    constexpr int NMAT = DUAL ? 2 : 1;
+    __shared__ float red[SK_WARPS][NMAT][ROWS][SK_COLS + 1];
+
+    const int g_idx = blockIdx.y;
+    int row_lo = 0, row_hi = a.M;
+    if (a.group_offsets) {
+        row_lo = a.group_offsets[g_idx];
+        row_hi = a.group_offsets[g_idx + 1];
+    }
+    if (row_lo >= row_hi) return;
+    const int n0 = blockIdx.x * SK_COLS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    const __nv_bfloat16* Wg = a.W + (size_t)g_idx * a.w_group_stride;
+    // weight rows of this thread: columns n0 + g and n0 + g + 8 (clamped; never stored when out of range)
+    const int c0 = min(n0 + g, a.N - 1), c1 = min(n0 + g + 8, a.N - 1);
+    const __nv_bfloat16* w0 = Wg + (size_t)c0 * a.ldw + t * 8;
+    const __nv_bfloat16* w1 = Wg + (size_t)c1 * a.ldw + t * 8;
+    const __nv_bfloat16* u0 = DUAL ? Wg + (size_t)(a.N + c0) * a.ldw + t * 8 : nullptr;
+    const __nv_bfloat16* u1 = DUAL ? Wg + (size_t)(a.N + c1) * a.ldw + t * 8 : nullptr;
+    const int k_steps = (a.K + 31) / 32;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+    for (int chunk = row_lo; chunk < row_hi; chunk += ROWS) {
+        const int rows = min(ROWS, row_hi - chunk);
+        const int nta = (rows + 7) >> 3;
+        // activation rows of this thread: token g of every n-tile
+        const __nv_bfloat16* xp[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int m = chunk + nt * 8 + g;
+            xp[nt] = nullptr;
+            if (m < row_hi) xp[nt] = a.X + (size_t)(a.x_rows ? a.x_rows[m] : m) * a.ldx + t * 8;
+        }
+        float acc[NMAT][NT][4];
+#pragma unroll
+        for (int i = 0; i < NMAT; ++i)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][nt][j] = 0.f;
+
+        for (int s = warp; s < k_steps; s += SK_WARPS) {
+            const int k = s * 32;
+            const bool live = k + t * 8 < a.K;
+            const uint4 wa = live ? ld16(w0 + k) : zero4;
+            const uint4 wb = live ? ld16(w1 + k) : zero4;
+            uint4 ua = zero4, ub = zero4;
+            if (DUAL && live) {
+                ua = ld16(u0 + k);
+                ub = ld16(u1 + k);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                if (nt < nta) {
+                    const uint4 x = (live && xp[nt]) ? ld16(xp[nt] + k) : zero4;
+                    mma_bf16_16816(acc[0][nt], wa.x, wb.x, wa.y, wb.y, x.x, x.y);
+                    mma_bf16_16816(acc[0][nt], wa.z, wb.z, wa.w, wb.w, x.z, x.w);
+                    if (DUAL) {
+                        mma_bf16_16816(acc[1][nt], ua.x, ub.x, ua.y, ub.y, x.x, x.y);
+                        mma_bf16_16816(acc[1][nt], ua.z, ub.z, ua.w, ub.w, x.z, x.w);
+                    }
+                }
+            }
+        }
+        // partial sums of this warp: d0 (col g, token 2t), d1 (col g, token 2t+1), d2/d3 the same for col g+8
+        __syncthreads();   // the previous chunk's reduction has been read
+#pragma unroll
+        for (int i = 0; i < NMAT; ++i)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                red[warp][i][nt * 8 + 2 * t][g] = acc[i][nt][0];
+                red[warp][i][nt * 8 + 2 * t + 1][g] = acc[i][nt][1];
+                red[warp][i][nt * 8 + 2 * t][g + 8] = acc[i][nt][2];
+                red[warp][i][nt * 8 + 2 * t + 1][g + 8] = acc[i][nt][3];
+            }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < rows * SK_COLS; idx += blockDim.x) {
+            const int r = idx / SK_COLS, c = idx - r * SK_COLS;
+            if (n0 + c >= a.N) continue;
+            float v = 0.f, v2 = 0.f;
+#pragma unroll
+            for (int w = 0; w < SK_WARPS; ++w) {
+                v += red[w][0][r][c];
+                if (DUAL) v2 += red[w][NMAT - 1][r][c];
+            }
+            if (DUAL) v = v / (1.0f + expf(-v)) * v2;
+            stf(static_cast<TY*>(a.Y) + (size_t)(chunk + r) * a.ldy + n0 + c, v);
+        }
+    }
+}
+
+template <int NT>
+static int skinny_launch_nt(const SkinnyArgs& a, int out_kind, cudaStream_t s) {
+    dim3 grid((a.N + SK_COLS - 1) / SK_COLS, a.G);
+    const int threads = SK_WARPS * 32;
+    if (out_kind == 0)
+        gemm_skinny_kernel<NT, false, __nv_bfloat16><<<grid, threads, 0, s>>>(a);
+    else if (out_kind == 1)
+        gemm_skinny_kernel<NT, false, float><<<grid, threads, 0, s>>>(a);
+    else if (out_kind == 2)
+        gemm_skinny_kernel<NT, true, __nv_bfloat16><<<grid, threads, 0, s>>>(a);
+    else
+        return TB_ERR_ARG;
+    return tb_last_error();
+}
+
+extern "C" {
+// out_kind: 0 = bfloat16 out, 1 = float out, 2 = swiglu pair (bfloat16 out).  M is the number of rows
+// (with group_offsets: an upper bound on the rows of any one group is min(M, rows of that group)).
+int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
+                        long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G, int out_kind,
+                        cudaStream_t s) {
+    if (M < 0 || N <= 0 || K <= 0 || G <= 0) return TB_ERR_ARG;
+    if (K % 8 || ldx % 8 || ldw % 8 || (w_group_stride % 8)) return TB_ERR_UNSUPPORTED;
+    if (((uintptr_t)X | (uintptr_t)W) & 15) return TB_ERR_UNSUPPORTED;
+    if (M == 0) return 0;
+    SkinnyArgs a{(const __nv_bfloat16*)X, x_rows, (const __nv_bfloat16*)W, Y, group_offsets, w_group_stride,
+                 ldx, ldw, ldy, M, N, K, G};
+    if (M <= 8) return skinny_launch_nt<1>(a, out_kind, s);
+    if (M <= 16) return skinny_launch_nt<2>(a, out_kind, s);
+    return skinny_launch_nt<4>(a, out_kind, s);
+}
+}

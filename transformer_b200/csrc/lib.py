@@ -28,6 +28,8 @@ _SIGNATURES: Dict[str, str] = {
     "tb_rope_cache_f32": "ppppippppiiiii", "tb_rope_cache_bf16": "ppppippppiiiii",
     "tb_attention_f32": "ppppppppppiiiiiiiif", "tb_attention_bf16": "ppppppppppiiiiiiiif",
     "tb_gemm_simt_f32": "pppppliiiiiiii".replace(" ", ""), "tb_gemm_simt_bf16": "pppppliiiiiiii",
+    "tb_gemm_skinny_bf16": "pppppliiiiiiii",
+    "tb_attention_decode_f32": "ppppppppiiiiiiif", "tb_attention_decode_bf16": "ppppppppiiiiiiif",
     "tb_router_f32": "pppppiiii", "tb_router_bf16": "pppppiiii",
     "tb_moe_dispatch": "ppppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
@@ -79,6 +81,20 @@ def _error_text(code: int) -> str:
 
 
 launch_count = 0     # launchers called so far (a launcher may start more than one kernel)
+
+
+def try_call(name: str, *args) -> bool:
+    """Like :func:`call`, but a kernel that refuses the sizes (TB_ERR_UNSUPPORTED) answers False
+    instead of raising, so the caller can take the general kernel."""
+    global launch_count
+    fn = getattr(library(), name)
+    rc = fn(*args, torch.cuda.current_stream().cuda_stream)
+    if rc == -2:
+        return False
+    if rc != 0:
+        raise KernelError(f"{name}: {_error_text(rc)}")
+    launch_count += 1
+    return True
 
 
 def call(name: str, *args) -> None:

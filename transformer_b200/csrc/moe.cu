@@ -6,10 +6,10 @@
 // leaves the device: a step has no synchronisation point.
 #include "common.cuh"
 
-#define ROUTER_WARPS 4
+#define ROUTER_WARPS 16
 #define ROUTER_MAX_E 1024
 
-// One warp per token.
+// One block per token, one warp per expert (warps loop when there are more experts than warps).
 //   logits[e] = x1 . Wr[e]                       float accumulation, kept in float
 //   keep the k largest, ties to the lower expert (the reference sorts descending, compute.rs:381)
 //   w_j = exp(v_j - v_0) / sum_kept exp(v_i - v_0)    softmax over the kept logits (compute.rs:383-392)
@@ -18,23 +18,34 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restrict__ topk_idx,
               float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d, int E, int k) {
-    extern __shared__ float sm[];   // [ROUTER_WARPS][E]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * ROUTER_WARPS + warp;
-    if (t >= nt) return;
-    float* lg = sm + warp * E;
+    constexpr int EPL = Vec16<T>::N;
+    extern __shared__ float lg[];   // [E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int t = blockIdx.x;
     const T* xr = x1 + (size_t)t * d;
-    for (int e = 0; e < E; ++e) {
+    const bool vec = (d % EPL) == 0;
+    for (int e = warp; e < E; e += nwarps) {
         const T* w = wr + (size_t)e * d;
         float acc = 0.f;
-        for (int c = lane; c < d; c += 32) acc += ldf(xr + c) * ldf(w + c);
+        if (vec) {
+            for (int c = lane * EPL; c < d; c += 32 * EPL) {
+                float xf[EPL], wf[EPL];
+                Vec16<T>::load(xr + c, xf);
+                Vec16<T>::load(w + c, wf);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) acc += xf[i] * wf[i];
+            }
+        } else {
+            for (int c = lane; c < d; c += 32) acc += ldf(xr + c) * ldf(w + c);
+        }
         acc = warp_sum(acc);
         if (lane == 0) {
             lg[e] = acc;
             if (logits_out) logits_out[(size_t)t * E + e] = acc;
         }
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     float v0 = 0.f, sum = 0.f;
     for (int j = 0; j < k; ++j) {
         float best = -INFINITY;
@@ -46,7 +57,6 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
                 bi = e;
             }
         }
-        // never-chosen sentinel: an expert already taken is marked by NaN below
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -124,8 +134,9 @@ static int router_launch(const void* x1, const void* wr, int* topk_idx, float* t
     if (nt < 0 || d <= 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
     if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
-    const int blocks = (nt + ROUTER_WARPS - 1) / ROUTER_WARPS;
-    router_kernel<T><<<blocks, ROUTER_WARPS * 32, (size_t)ROUTER_WARPS * E * sizeof(float), s>>>(
+    int warps = E < ROUTER_WARPS ? E : ROUTER_WARPS;
+    if (nt >= 1024 && warps > 4) warps = 4;   // many tokens: fewer, longer-lived warps per token
+    router_kernel<T><<<nt, warps * 32, (size_t)E * sizeof(float), s>>>(
         (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k);
     return tb_last_error();
 }

@@ -62,6 +62,9 @@ class Attention(Mixer):
                  lib.ptr(table), ctx.max_pages, lib.ptr(cos), lib.ptr(sin), lib.ptr(kc), lib.ptr(vc),
                  nt, self.nh, self.nkvh, self.dh, half)
         o = ctx.scratch("attn.o", (nt, self.nh * self.dh), self.dtype)
+        if ctx.decode and self._decode_kernel(ctx, qkv, o, cache, table, nt, sfx):
+            matmul_nt(o, self.weights["wo"], out)
+            return
         tiles = ctx.attention_tiles(self.nh, self.nkvh)
         splits = ctx.attention_splits(tiles.count, self.nh, self.nkvh)
         partial = None
@@ -72,3 +75,16 @@ class Attention(Mixer):
                  lib.ptr(partial), tiles.count, nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh,
                  splits, self.scale)
         matmul_nt(o, self.weights["wo"], out)
+
+    def _decode_kernel(self, ctx, qkv, o, cache, table, nt, sfx) -> bool:
+        """One token per sequence: the kernel that streams the cache.  False if it refuses the head size."""
+        group = self.nh // self.nkvh
+        gc = 1 if group == 1 else 2 if group == 2 else 4
+        blocks = nt * self.nkvh * ((group + gc - 1) // gc)
+        splits = int(max(1, min(32, (3 * ctx.engine.sm_count + blocks - 1) // blocks)))
+        partial = None
+        if splits > 1:
+            partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
+        return lib.try_call("tb_attention_decode_" + sfx, lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                            lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
+                            ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, self.scale)

@@ -11,7 +11,7 @@ import torch
 
 from ..csrc import lib
 from .base import FEED_FORWARDS, FeedForward, ParamDecl
-from .linear import gemm_simt, matmul_nt
+from .linear import grouped_matmul, matmul_nt
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -30,7 +30,7 @@ class DenseSwiGLU(FeedForward):
     def forward(self, ctx, x1, out) -> None:
         nt = x1.shape[0]
         h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
-        gemm_simt(x1, self.weights["wgu"], h, out_kind=2)
+        grouped_matmul(x1, self.weights["wgu"], h, swiglu=True)
         matmul_nt(h, self.weights["wd"], out)
 
 
@@ -80,9 +80,9 @@ class MoE(FeedForward):
         lib.call("tb_moe_dispatch", lib.ptr(idx), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
                  M, self.k, self.E)
         h = ctx.scratch("moe.h", (M, self.di), self.dtype)
-        gemm_simt(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
-                  out_kind=2)
+        grouped_matmul(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
+                       swiglu=True)
         y = ctx.scratch("moe.y", (M, self.d), self.dtype)
-        gemm_simt(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E, out_kind=0)
+        grouped_matmul(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E)
         lib.call("tb_moe_combine_" + sfx, lib.ptr(y), lib.ptr(pair_row), lib.ptr(w), lib.ptr(out), nt, self.d,
                  self.k)

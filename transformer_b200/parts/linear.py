@@ -28,13 +28,44 @@ def gemm_simt(a, w, out, *, a_rows=None, group_offsets=None, groups=1, rows=None
              lib.ptr(group_offsets), stride, a.stride(0), ldb, out.stride(0), M, N, K, groups, out_kind)
 
 
+SKINNY_MAX_ROWS = 64       # dense: up to this many rows the weight-streaming kernel is used
+SKINNY_MAX_PAIRS = 512     # grouped: up to this many rows over all groups
+
+
+def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kind=0) -> bool:
+    """The decode kernel (bfloat16, tensor cores, weights streamed once).  False if it refuses the sizes."""
+    M, K, N = out.shape[0], a.shape[-1], out.shape[-1]
+    if w.dim() == 3:
+        stride, ldw = w.stride(0), w.stride(1)
+    else:
+        stride, ldw = 0, w.stride(0)
+    assert a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    return lib.try_call("tb_gemm_skinny_bf16", lib.ptr(a), lib.ptr(a_rows), lib.ptr(w), lib.ptr(out),
+                        lib.ptr(group_offsets), stride, a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind)
+
+
 def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out = a @ w.T for one dense weight; out has a's type, or float (logits)."""
-    if a.shape[0] == 0:
+    M = a.shape[0]
+    if M == 0:
         return
+    to_float = out.dtype == torch.float32
     if a.dtype == torch.float32:
         gemm_simt(a, w, out, out_kind=0)
-    elif out.dtype == torch.float32:
+        return
+    if M <= SKINNY_MAX_ROWS and gemm_skinny(a, w, out, out_kind=1 if to_float else 0):
+        return
+    if to_float:
         gemm_simt(a, w, out, out_kind=1)
     else:
         torch.mm(a, w.t(), out=out)
+
+
+def grouped_matmul(a, w, out, *, a_rows=None, group_offsets=None, groups=1, swiglu=False) -> None:
+    """out[m] = a[a_rows[m] or m] . w[g(m)]^T over rows sorted by group; with swiglu, w[g] holds gate rows
+    then up rows and out = silu(gate) * up."""
+    kind = 2 if swiglu else 0
+    if a.dtype == torch.bfloat16 and out.shape[0] <= SKINNY_MAX_PAIRS and \
+            gemm_skinny(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind):
+        return
+    gemm_simt(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind)
