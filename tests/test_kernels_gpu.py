@@ -49,7 +49,7 @@ def test_add_rmsnorm(dtype, d):
     w = _rand((d,), torch.float32, 3)
     y = torch.empty((n, d), dtype=dtype, device="cuda")
     x_in = x.clone()
-    lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), delta.data_ptr(), 0, w.data_ptr(), eps,
+    lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), delta.data_ptr(), 0, 0, 0, 0, 0, w.data_ptr(), eps,
              y.data_ptr(), n, d)
     v = x_in.double() + delta.double()
     assert torch.allclose(x.double(), v, atol=1e-6), "the stream is updated in place with a float sum"
@@ -59,7 +59,7 @@ def test_add_rmsnorm(dtype, d):
     rows = torch.tensor([6, 0, 6], dtype=torch.int32, device="cuda")
     y2 = torch.empty((3, d), dtype=dtype, device="cuda")
     before = x.clone()
-    lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), 0, rows.data_ptr(), w.data_ptr(), eps,
+    lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), 0, 0, 0, 0, 0, rows.data_ptr(), w.data_ptr(), eps,
              y2.data_ptr(), 3, d)
     assert torch.equal(x, before)
     ref2 = P.rms_norm(before[rows.long()].double().cpu(), w.double().cpu(), eps)

@@ -7,10 +7,10 @@
 //
 //   * a block = (token, key/value head, up to GC of its query heads, one slice of the keys);
 //   * a key row is read by a "sub-warp" of dh / EPL lanes, each lane one 16-byte load (EPL = 8
-//     bfloat16 or 4 float values); the 256 threads of a block form 256 / (dh / EPL) sub-warps that
+//     bfloat16 or 4 float values); the 128 threads of a block form 128 / (dh / EPL) sub-warps that
 //     take consecutive keys, so a block streams whole 64-token pages with full-width loads;
 //   * every sub-warp runs its own online softmax (running max, sum, output slice) over its keys,
-//     four keys at a time; the sub-warps are merged once at the end through shared memory;
+//     four keys at a time, the next four already in flight; the sub-warps are merged once at the end through shared memory;
 //   * with several key slices the block writes (unnormalised output, max, sum) per slice in the
 //     layout of the general kernel and attention_merge_kernel combines them.
 //
@@ -19,7 +19,7 @@
 // the general kernel.
 #include "attention_kernels.cuh"
 
-#define AD_THREADS 256
+#define AD_THREADS 128
 #define AD_UNROLL 4
 
 struct DecodeArgs {
@@ -80,27 +80,46 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(const Deco
     }
     const T* kc = static_cast<const T*>(a.kc);
     const T* vc = static_cast<const T*>(a.vc);
-    const int* pt = a.page_table + (size_t)b * a.max_pages;
+    // the pages of this block's key slice, once, into shared memory
+    int* sm_pages = reinterpret_cast<int*>(sm_l + nsw * GC);
+    {
+        const int* pt = a.page_table + (size_t)b * a.max_pages;
+        const int p_lo = k_lo / TB_PAGE, p_hi = (k_hi + TB_PAGE - 1) / TB_PAGE;
+        for (int i = p_lo + threadIdx.x; i < p_hi; i += blockDim.x) sm_pages[i - p_lo] = pt[i];
+    }
+    __syncthreads();
+    const int page0 = k_lo / TB_PAGE;
+    const size_t lane_off = (size_t)li * EPL;
 
+    // raw 16-byte loads for the AD_UNROLL keys of one round; keys past the slice load nothing
+    auto fetch = [&](int base, uint4 (&kr)[AD_UNROLL], uint4 (&vr)[AD_UNROLL]) {
+#pragma unroll
+        for (int u = 0; u < AD_UNROLL; ++u) {
+            const int key = base + sw + u * nsw;
+            kr[u] = make_uint4(0u, 0u, 0u, 0u);
+            vr[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (key < k_hi) {
+                const int page = sm_pages[key / TB_PAGE - page0];
+                const size_t off = (((size_t)page * a.nkvh + g) * TB_PAGE + (key % TB_PAGE)) * dh + lane_off;
+                kr[u] = *reinterpret_cast<const uint4*>(kc + off);
+                vr[u] = *reinterpret_cast<const uint4*>(vc + off);
+            }
+        }
+    };
+
+    uint4 kr[AD_UNROLL], vr[AD_UNROLL];
+    fetch(k_lo, kr, vr);
     // the trip count is the same for every lane of a warp (the shuffles below need all of them)
     for (int base = k_lo; base < k_hi; base += nsw * AD_UNROLL) {
-        const int k0 = base + sw;
         float kf[AD_UNROLL][EPL], vf[AD_UNROLL][EPL];
         bool live[AD_UNROLL];
 #pragma unroll
         for (int u = 0; u < AD_UNROLL; ++u) {
-            const int key = k0 + u * nsw;
-            live[u] = key < k_hi;
-            if (live[u]) {
-                const int page = pt[key / TB_PAGE];
-                const size_t off = (((size_t)page * a.nkvh + g) * TB_PAGE + (key % TB_PAGE)) * dh + li * EPL;
-                Vec16<T>::load(kc + off, kf[u]);
-                Vec16<T>::load(vc + off, vf[u]);
-            } else {
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) kf[u][e] = vf[u][e] = 0.f;
-            }
+            live[u] = base + sw + u * nsw < k_hi;
+            Vec16<T>::unpack(kr[u], kf[u]);
+            Vec16<T>::unpack(vr[u], vf[u]);
         }
+        fetch(base + nsw * AD_UNROLL, kr, vr);     // the next round's loads fly while this one is computed
 #pragma unroll
         for (int hc = 0; hc < GC; ++hc) {
             if (hc >= nheads) continue;
@@ -178,7 +197,7 @@ template <typename T, int GC>
 static int decode_launch_gc(const DecodeArgs& a, int nt, cudaStream_t s) {
     constexpr int EPL = Vec16<T>::N;
     const int tpk = a.dh / EPL, nsw = AD_THREADS / tpk;
-    const size_t smem = ((size_t)nsw * GC * a.dh + 2 * (size_t)nsw * GC) * sizeof(float);
+    const size_t smem = ((size_t)nsw * GC * a.dh + 2 * (size_t)nsw * GC) * sizeof(float) + (size_t)a.max_pages * sizeof(int);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<T, GC>,

@@ -76,7 +76,9 @@ template <typename T> struct Vec16;
 template <> struct Vec16<__nv_bfloat16> {
     static constexpr int N = 8;
     __device__ __forceinline__ static void load(const __nv_bfloat16* p, float (&f)[8]) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        unpack(*reinterpret_cast<const uint4*>(p), f);
+    }
+    __device__ __forceinline__ static void unpack(const uint4& v, float (&f)[8]) {
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -89,8 +91,11 @@ template <> struct Vec16<__nv_bfloat16> {
 template <> struct Vec16<float> {
     static constexpr int N = 4;
     __device__ __forceinline__ static void load(const float* p, float (&f)[4]) {
-        const float4 v = *reinterpret_cast<const float4*>(p);
-        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+        unpack(*reinterpret_cast<const uint4*>(p), f);
+    }
+    __device__ __forceinline__ static void unpack(const uint4& v, float (&f)[4]) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+        f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
     }
 };
 

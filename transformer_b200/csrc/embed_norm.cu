@@ -14,13 +14,18 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 }
 
 // Row r = rows ? rows[i] : i.
-//   v = x[r] + (delta ? delta[r] : 0)                      float sum
-//   if (!rows && delta) x[r] = v                           the stream is updated in place
+//   v = x[r] + delta(r)                                    float sum
+//   if (!rows && there is a delta) x[r] = v                the stream is updated in place
 //   y[i] = v / sqrt(mean(v^2) + eps) * w                   statistics in float, one rounding to T
+// delta(r) is delta[r] (a part's output), or, when wy is given, the weighted sum of rows of wy:
+//   sum_j topk_w[r, j] * wy[pair_row[r * k + j]]           j ascending, in float
+// which is the combine of the experts' outputs (compute.rs:329-330) fused into the norm that follows.
 // (call sites of rms_norm: models/llama/common/src/compute.rs:207,275,362; the residual sum is the
 //  beta = 1 of the output products, :270,:330.)
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                   const T* __restrict__ wy, const int* __restrict__ pair_row,
+                                   const float* __restrict__ topk_w, int k,
                                    const int* __restrict__ rows, const float* __restrict__ w,
                                    float eps, T* __restrict__ y, int d) {
     __shared__ float red[33];
@@ -28,11 +33,19 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     const int r = rows ? rows[i] : i;
     float* xr = x + (size_t)r * d;
     const T* dr = delta ? delta + (size_t)r * d : nullptr;
-    const bool write_back = (rows == nullptr) && (delta != nullptr);
+    const bool has_delta = dr != nullptr || wy != nullptr;
+    const bool write_back = (rows == nullptr) && has_delta;
+    auto delta_at = [&](int c) -> float {
+        if (dr) return ldf(dr + c);
+        float acc = 0.f;
+        for (int j = 0; j < k; ++j)
+            acc += topk_w[(size_t)r * k + j] * ldf(wy + (size_t)pair_row[(size_t)r * k + j] * d + c);
+        return acc;
+    };
     float ss = 0.f;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float v = xr[c];
-        if (dr) v += ldf(dr + c);
+        if (has_delta) v += delta_at(c);
         if (write_back) xr[c] = v;
         ss += v * v;
     }
@@ -41,7 +54,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     T* yr = y + (size_t)i * d;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float v = xr[c];
-        if (dr && !write_back) v += ldf(dr + c);
+        if (has_delta && !write_back) v += delta_at(c);
         stf(yr + c, v * rs * w[c]);
     }
 }
@@ -54,12 +67,15 @@ static int embed_launch(const int* tokens, const void* table, float* x, int nt, 
     return tb_last_error();
 }
 template <typename T>
-static int add_rmsnorm_launch(float* x, const void* delta, const int* rows, const float* w, float eps,
+static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const int* pair_row,
+                              const float* topk_w, int k, const int* rows, const float* w, float eps,
                               void* y, int n_out, int d, cudaStream_t s) {
     if (n_out < 0 || d <= 0) return TB_ERR_ARG;
+    if (wy && (delta || !pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
     if (n_out == 0) return 0;
     int threads = d >= 2048 ? 512 : 256;
-    add_rmsnorm_kernel<T><<<n_out, threads, 0, s>>>(x, (const T*)delta, rows, w, eps, (T*)y, d);
+    add_rmsnorm_kernel<T><<<n_out, threads, 0, s>>>(x, (const T*)delta, (const T*)wy, pair_row, topk_w, k, rows, w, eps,
+                                                   (T*)y, d);
     return tb_last_error();
 }
 
@@ -70,12 +86,12 @@ int tb_embed_f32(const int* tokens, const void* table, float* x, int nt, int d, 
 int tb_embed_bf16(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
     return embed_launch<__nv_bfloat16>(tokens, table, x, nt, d, s);
 }
-int tb_add_rmsnorm_f32(float* x, const void* delta, const int* rows, const float* w, float eps, void* y,
-                       int n_out, int d, cudaStream_t s) {
-    return add_rmsnorm_launch<float>(x, delta, rows, w, eps, y, n_out, d, s);
+int tb_add_rmsnorm_f32(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w, int k,
+                       const int* rows, const float* w, float eps, void* y, int n_out, int d, cudaStream_t s) {
+    return add_rmsnorm_launch<float>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, s);
 }
-int tb_add_rmsnorm_bf16(float* x, const void* delta, const int* rows, const float* w, float eps, void* y,
-                        int n_out, int d, cudaStream_t s) {
-    return add_rmsnorm_launch<__nv_bfloat16>(x, delta, rows, w, eps, y, n_out, d, s);
+int tb_add_rmsnorm_bf16(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w, int k,
+                        const int* rows, const float* w, float eps, void* y, int n_out, int d, cudaStream_t s) {
+    return add_rmsnorm_launch<__nv_bfloat16>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, s);
 }
 }

@@ -51,11 +51,14 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
     return *reinterpret_cast<const uint4*>(p);
 }
 
-template <int NT, bool DUAL, typename TY>
-__global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const SkinnyArgs a) {
+// WK warps split K, WN warps take 16 columns each: a block covers 16 * WN columns.
+// UNR k-steps are loaded before any of them is multiplied, so that every thread keeps several
+// 16-byte loads in flight (the step is bound by memory latency x bytes in flight otherwise).
+template <int NT, bool DUAL, typename TY, int WK, int WN, int UNR>
+__global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyArgs a) {
     constexpr int ROWS = 8 * NT;
     constexpr int NMAT = DUAL ? 2 : 1;
-    __shared__ float red[SK_WARPS][NMAT][ROWS][SK_COLS + 1];
+    __shared__ float red[WN][WK][NMAT][ROWS][SK_COLS + 1];
 
     const int g_idx = blockIdx.y;
     int row_lo = 0, row_hi = a.M;
@@ -64,8 +67,9 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const Skinny
         row_hi = a.group_offsets[g_idx + 1];
     }
     if (row_lo >= row_hi) return;
-    const int n0 = blockIdx.x * SK_COLS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wk = warp % WK, wn = warp / WK;
+    const int n0 = (blockIdx.x * WN + wn) * SK_COLS;
     const int g = lane >> 2, t = lane & 3;
 
     const __nv_bfloat16* Wg = a.W + (size_t)g_idx * a.w_group_stride;
@@ -97,25 +101,33 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const Skinny
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][nt][j] = 0.f;
 
-        for (int s = warp; s < k_steps; s += SK_WARPS) {
-            const int k = s * 32;
-            const bool live = k + t * 8 < a.K;
-            const uint4 wa = live ? ld16(w0 + k) : zero4;
-            const uint4 wb = live ? ld16(w1 + k) : zero4;
-            uint4 ua = zero4, ub = zero4;
-            if (DUAL && live) {
-                ua = ld16(u0 + k);
-                ub = ld16(u1 + k);
+        for (int s0 = wk; s0 < k_steps; s0 += WK * UNR) {
+            uint4 wa[UNR], wb[UNR], ua[DUAL ? UNR : 1], ub[DUAL ? UNR : 1], xv[UNR][NT];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const int k = (s0 + u * WK) * 32;
+                const bool live = k + t * 8 < a.K;      // also false past the last step
+                wa[u] = live ? ld16(w0 + k) : zero4;
+                wb[u] = live ? ld16(w1 + k) : zero4;
+                if (DUAL) {
+                    ua[u] = live ? ld16(u0 + k) : zero4;
+                    ub[u] = live ? ld16(u1 + k) : zero4;
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) xv[u][nt] = (live && nt < nta && xp[nt]) ? ld16(xp[nt] + k) : zero4;
             }
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                if (nt < nta) {
-                    const uint4 x = (live && xp[nt]) ? ld16(xp[nt] + k) : zero4;
-                    mma_bf16_16816(acc[0][nt], wa.x, wb.x, wa.y, wb.y, x.x, x.y);
-                    mma_bf16_16816(acc[0][nt], wa.z, wb.z, wa.w, wb.w, x.z, x.w);
-                    if (DUAL) {
-                        mma_bf16_16816(acc[1][nt], ua.x, ub.x, ua.y, ub.y, x.x, x.y);
-                        mma_bf16_16816(acc[1][nt], ua.z, ub.z, ua.w, ub.w, x.z, x.w);
+            for (int u = 0; u < UNR; ++u) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    if (nt < nta) {
+                        const uint4 x = xv[u][nt];
+                        mma_bf16_16816(acc[0][nt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, x.x, x.y);
+                        mma_bf16_16816(acc[0][nt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, x.z, x.w);
+                        if (DUAL) {
+                            mma_bf16_16816(acc[1][nt], ua[u].x, ub[u].x, ua[u].y, ub[u].y, x.x, x.y);
+                            mma_bf16_16816(acc[1][nt], ua[u].z, ub[u].z, ua[u].w, ub[u].w, x.z, x.w);
+                        }
                     }
                 }
             }
@@ -126,40 +138,51 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const Skinny
         for (int i = 0; i < NMAT; ++i)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                red[warp][i][nt * 8 + 2 * t][g] = acc[i][nt][0];
-                red[warp][i][nt * 8 + 2 * t + 1][g] = acc[i][nt][1];
-                red[warp][i][nt * 8 + 2 * t][g + 8] = acc[i][nt][2];
-                red[warp][i][nt * 8 + 2 * t + 1][g + 8] = acc[i][nt][3];
+                red[wn][wk][i][nt * 8 + 2 * t][g] = acc[i][nt][0];
+                red[wn][wk][i][nt * 8 + 2 * t + 1][g] = acc[i][nt][1];
+                red[wn][wk][i][nt * 8 + 2 * t][g + 8] = acc[i][nt][2];
+                red[wn][wk][i][nt * 8 + 2 * t + 1][g + 8] = acc[i][nt][3];
             }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < rows * SK_COLS; idx += blockDim.x) {
-            const int r = idx / SK_COLS, c = idx - r * SK_COLS;
-            if (n0 + c >= a.N) continue;
+        const int nb0 = blockIdx.x * WN * SK_COLS;
+        for (int idx = threadIdx.x; idx < rows * SK_COLS * WN; idx += blockDim.x) {
+            const int r = idx / (SK_COLS * WN), cc = idx - r * (SK_COLS * WN);
+            const int w_n = cc / SK_COLS, c = cc - w_n * SK_COLS;
+            if (nb0 + cc >= a.N) continue;
             float v = 0.f, v2 = 0.f;
 #pragma unroll
-            for (int w = 0; w < SK_WARPS; ++w) {
-                v += red[w][0][r][c];
-                if (DUAL) v2 += red[w][NMAT - 1][r][c];
+            for (int w = 0; w < WK; ++w) {
+                v += red[w_n][w][0][r][c];
+                if (DUAL) v2 += red[w_n][w][NMAT - 1][r][c];
             }
             if (DUAL) v = v / (1.0f + expf(-v)) * v2;
-            stf(static_cast<TY*>(a.Y) + (size_t)(chunk + r) * a.ldy + n0 + c, v);
+            stf(static_cast<TY*>(a.Y) + (size_t)(chunk + r) * a.ldy + nb0 + cc, v);
         }
     }
 }
 
+template <int NT, bool DUAL, typename TY>
+static int skinny_launch_shape(const SkinnyArgs& a, cudaStream_t s) {
+    // long rows: all 8 warps of a block share 16 columns and split K;
+    // short rows (an expert's down projection): 4 column groups x 2 warps on K
+    if (a.K >= 2048) {
+        constexpr int WK = 8, WN = 1, UNR = NT >= 4 ? 2 : 4;
+        dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
+        gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR><<<grid, WK * WN * 32, 0, s>>>(a);
+    } else {
+        constexpr int WK = 2, WN = 4, UNR = NT >= 4 ? 2 : 4;
+        dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
+        gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR><<<grid, WK * WN * 32, 0, s>>>(a);
+    }
+    return tb_last_error();
+}
+
 template <int NT>
 static int skinny_launch_nt(const SkinnyArgs& a, int out_kind, cudaStream_t s) {
-    dim3 grid((a.N + SK_COLS - 1) / SK_COLS, a.G);
-    const int threads = SK_WARPS * 32;
-    if (out_kind == 0)
-        gemm_skinny_kernel<NT, false, __nv_bfloat16><<<grid, threads, 0, s>>>(a);
-    else if (out_kind == 1)
-        gemm_skinny_kernel<NT, false, float><<<grid, threads, 0, s>>>(a);
-    else if (out_kind == 2)
-        gemm_skinny_kernel<NT, true, __nv_bfloat16><<<grid, threads, 0, s>>>(a);
-    else
-        return TB_ERR_ARG;
-    return tb_last_error();
+    if (out_kind == 0) return skinny_launch_shape<NT, false, __nv_bfloat16>(a, s);
+    if (out_kind == 1) return skinny_launch_shape<NT, false, float>(a, s);
+    if (out_kind == 2) return skinny_launch_shape<NT, true, __nv_bfloat16>(a, s);
+    return TB_ERR_ARG;
 }
 
 extern "C" {

@@ -10,13 +10,18 @@
 // Cache of one layer: K and V each [pages, nkvh, TB_PAGE, dh].
 #include "common.cuh"
 
+#define ROPE_HEADS 4   // heads per block
+
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ tok_seq,
                                   const int* __restrict__ tok_pos, const int* __restrict__ page_table,
                                   int max_pages, const float* __restrict__ cos_t,
                                   const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
                                   int nh, int nkvh, int dh, int half_pairing) {
+    // grid: (token, chunk of ROPE_HEADS heads out of q heads, k heads, v heads in that order)
     const int t = blockIdx.x;
+    const int head_lo = blockIdx.y * ROPE_HEADS;
+    const int head_hi = min(head_lo + ROPE_HEADS, nh + 2 * nkvh);
     const int pos = tok_pos[t];
     const int half = dh >> 1;
     T* row = qkv + (size_t)t * (nh + 2 * nkvh) * dh;
@@ -27,9 +32,9 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ t
         const int page = page_table[(size_t)tok_seq[t] * max_pages + pos / TB_PAGE];
         cache_row = ((size_t)page * nkvh * TB_PAGE + (pos % TB_PAGE)) * dh;  // + g * TB_PAGE * dh
     }
-    const int n_rot = (nh + nkvh) * half;
-    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
-        const int head = idx / half, i = idx - head * half;
+    const int rot_hi = min(head_hi, nh + nkvh);
+    for (int idx = threadIdx.x; idx < (rot_hi - head_lo) * half; idx += blockDim.x) {
+        const int head = head_lo + idx / half, i = idx % half;
         const int i0 = half_pairing ? i : 2 * i;
         const int i1 = half_pairing ? i + half : 2 * i + 1;
         T* h = row + (size_t)head * dh;
@@ -46,11 +51,11 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ t
             stf(dst + i1, y1);
         }
     }
-    if (vc) {
-        const T* v = row + (size_t)(nh + nkvh) * dh;
-        for (int idx = threadIdx.x; idx < nkvh * dh; idx += blockDim.x) {
-            const int g = idx / dh, c = idx - g * dh;
-            vc[cache_row + (size_t)g * TB_PAGE * dh + c] = v[idx];
+    if (vc && head_hi > nh + nkvh) {
+        const int v_lo = max(head_lo, nh + nkvh);
+        for (int idx = threadIdx.x; idx < (head_hi - v_lo) * dh; idx += blockDim.x) {
+            const int head = v_lo + idx / dh, c = idx % dh;
+            vc[cache_row + (size_t)(head - nh - nkvh) * TB_PAGE * dh + c] = row[(size_t)head * dh + c];
         }
     }
 }
@@ -62,7 +67,8 @@ static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, 
     if (nt < 0 || nh <= 0 || nkvh <= 0 || dh <= 0 || (dh & 1)) return TB_ERR_ARG;
     if ((kc == nullptr) != (vc == nullptr)) return TB_ERR_ARG;
     if (nt == 0) return 0;
-    rope_cache_kernel<T><<<nt, 256, 0, s>>>((T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
+    dim3 grid(nt, (nh + 2 * nkvh + ROPE_HEADS - 1) / ROPE_HEADS);
+    rope_cache_kernel<T><<<grid, 128, 0, s>>>((T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
                                             (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
     return tb_last_error();
 }

@@ -19,7 +19,7 @@ import torch
 from ..cache.paged import Cache
 from ..cache.slots import CacheError
 from ..csrc import lib
-from ..parts.block import Layer
+from ..parts.block import Layer, resolve
 from ..parts.base import NORMS
 from ..parts.linear import matmul_nt
 from ..parts.spec import ModelSpec
@@ -253,6 +253,7 @@ class Engine:
             torch.empty((n_out, V), dtype=torch.float32, device=self.device)
         if n_out:
             xn = ctx.scratch("final.xn", (n_out, d), self.dtype)
+            pending = resolve(pending, self.final_norm, ctx.scratch("block.delta", (nt, d), self.dtype))
             self.final_norm.forward(ctx, x, pending, ctx.want_rows, xn)
             matmul_nt(xn, self.head, logits)
         return logits

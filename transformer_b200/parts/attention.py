@@ -81,7 +81,7 @@ class Attention(Mixer):
         group = self.nh // self.nkvh
         gc = 1 if group == 1 else 2 if group == 2 else 4
         blocks = nt * self.nkvh * ((group + gc - 1) // gc)
-        splits = int(max(1, min(32, (3 * ctx.engine.sm_count + blocks - 1) // blocks)))
+        splits = int(max(1, min(32, (8 * ctx.engine.sm_count) // blocks)))
         partial = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)

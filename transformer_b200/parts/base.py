@@ -15,7 +15,7 @@ Mixer         ``forward(ctx, x1, out, cache, state)``: reads the normed activati
               run's :class:`~transformer_b200.cache.paged.CacheView` (None if ``cache_need()``
               is None), ``state`` its per-sequence state tensor [slots, *shape] (None if
               ``state_need()`` is None); rows of ``state`` are addressed by ``ctx.slots``.
-FeedForward   ``forward(ctx, x1, out)``.
+FeedForward   ``forward(ctx, x1, out)``; may return a ``WeightedRows`` instead of filling ``out``.
 Position      owned by the mixer that uses it; for rotary encodings ``tables()`` gives cos and sin.
 ============  ===================================================================================
 
@@ -52,6 +52,17 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass
+class WeightedRows:
+    """A part's output that is not summed yet: out[t] = sum_j weights[t, j] * rows[index[t * k + j]].
+    A norm that sets ``takes_weighted_rows`` does the sum itself, in float, while it adds to the stream
+    (one kernel and one round trip through memory less); for any other norm the block sums first."""
+    rows: torch.Tensor        # [M, d]
+    index: torch.Tensor       # int32 [nt * k]
+    weights: torch.Tensor     # float [nt, k]
+    k: int
+
+
 class Part:
     def __init__(self, params: Dict[str, Any], dtype: torch.dtype, device: torch.device):
         self.params = dict(params)
@@ -72,6 +83,8 @@ class Part:
 
 
 class Norm(Part):
+    takes_weighted_rows = False
+
     def forward(self, ctx, x, delta, rows, y) -> None:
         raise NotImplementedError
 
@@ -88,7 +101,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    def forward(self, ctx, x1, out) -> None:
+    def forward(self, ctx, x1, out):
+        """Write the contribution into ``out`` and return None, or return a :class:`WeightedRows`
+        that stands for it (``out`` is then left alone)."""
         raise NotImplementedError
 
 

@@ -10,7 +10,7 @@ takes the pending delta of the block before it and returns its own.
 """
 from __future__ import annotations
 
-from .base import FEED_FORWARDS, MIXERS, NORMS
+from .base import FEED_FORWARDS, MIXERS, NORMS, WeightedRows
 
 
 class Layer:
@@ -34,9 +34,19 @@ class Layer:
         pending delta (the feed-forward's output)."""
         nt, d = x.shape
         x1 = ctx.scratch("block.x1", (nt, d), ctx.dtype)
-        self.mixer_norm.forward(ctx, x, pending, None, x1)
         delta = ctx.scratch("block.delta", (nt, d), ctx.dtype)
+        pending = resolve(pending, self.mixer_norm, delta)
+        self.mixer_norm.forward(ctx, x, pending, None, x1)
         self.mixer.forward(ctx, x1, delta, cache_view, state)
         self.feed_forward_norm.forward(ctx, x, delta, None, x1)
-        self.feed_forward.forward(ctx, x1, delta)
-        return delta
+        lazy = self.feed_forward.forward(ctx, x1, delta)
+        return delta if lazy is None else lazy
+
+
+def resolve(pending, norm, into):
+    """A pending WeightedRows stays as it is for a norm that sums it itself; else it is summed into ``into``."""
+    if isinstance(pending, WeightedRows) and not norm.takes_weighted_rows:
+        from .feed_forward import sum_weighted_rows
+        sum_weighted_rows(pending, into)
+        return into
+    return pending

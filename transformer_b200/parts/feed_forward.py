@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib
-from .base import FEED_FORWARDS, FeedForward, ParamDecl
+from .base import FEED_FORWARDS, FeedForward, ParamDecl, WeightedRows
 from .linear import grouped_matmul, matmul_nt
 
 
@@ -84,5 +84,12 @@ class MoE(FeedForward):
                        swiglu=True)
         y = ctx.scratch("moe.y", (M, self.d), self.dtype)
         grouped_matmul(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E)
-        lib.call("tb_moe_combine_" + sfx, lib.ptr(y), lib.ptr(pair_row), lib.ptr(w), lib.ptr(out), nt, self.d,
-                 self.k)
+        # the weighted sum over the chosen experts is left to the norm that follows (fused there)
+        return WeightedRows(y, pair_row, w, self.k)
+
+
+def sum_weighted_rows(wr: WeightedRows, out) -> None:
+    """out[t] = sum_j weights[t, j] * rows[index[t, j]], for a consumer that wants a plain tensor."""
+    nt, d = out.shape
+    lib.call("tb_moe_combine_" + lib.suffix(out.dtype), lib.ptr(wr.rows), lib.ptr(wr.index), lib.ptr(wr.weights),
+             lib.ptr(out), nt, d, wr.k)

@@ -4,12 +4,14 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib
-from .base import NORMS, Norm, ParamDecl
+from .base import NORMS, Norm, ParamDecl, WeightedRows
 
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """params: width, eps.  Statistics and the residual sum are float; one rounding at the store."""
+
+    takes_weighted_rows = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -21,5 +23,10 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, x, delta, rows, y) -> None:
         n_out = y.shape[0]
-        lib.call("tb_add_rmsnorm_" + lib.suffix(self.dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(rows),
-                 lib.ptr(self.weights["weight"]), self.eps, lib.ptr(y), n_out, self.width)
+        wy = idx = wts = None
+        k = 0
+        if isinstance(delta, WeightedRows):
+            wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
+        lib.call("tb_add_rmsnorm_" + lib.suffix(self.dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
+                 lib.ptr(wts), k, lib.ptr(rows), lib.ptr(self.weights["weight"]), self.eps, lib.ptr(y), n_out,
+                 self.width)
