@@ -317,3 +317,58 @@ def test_sampling_draws_from_the_stated_distribution(V, t, k, p):
         assert tok in kept, f"token {tok} is outside the kept set"
         j = kept.index(tok)
         assert cdf[j] - 1e-4 <= u <= cdf[j + 1] + 1e-4, f"u = {u}: token {tok} covers [{cdf[j]}, {cdf[j + 1]}]"
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (300, 688, 4096), (1000, 1376, 136), (77, 40, 688)])
+def test_gemm_tc_dense(M, N, K):
+    """The tcgen05 product against float64, bfloat16 and float outputs, with tails in M, N and K."""
+    lib = _lib()
+    from transformer_b200.parts.linear import gemm_tc
+    a, w = _rand((M, K), torch.bfloat16, 20), _rand((N, K), torch.bfloat16, 21, 0.1)
+    ref = a.double() @ w.double().T
+    for out_dtype, kind in ((torch.bfloat16, 0), (torch.float32, 1)):
+        out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+        assert gemm_tc(a, w, out, out_kind=kind)
+        assert lib.gemm_tc_status() == 0, "a wait inside the kernel gave up"
+        assert float((out.double() - ref).abs().max()) <= _tol(out_dtype, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("E,k,nt,d,di", [(4, 2, 300, 128, 96), (16, 4, 700, 256, 688), (3, 1, 130, 64, 200)])
+def test_gemm_tc_grouped_swiglu_and_down(E, k, nt, d, di):
+    """Experts through the prompt path: gather, grouped gate/up with swiglu, grouped down product."""
+    lib = _lib()
+    from transformer_b200.parts.linear import grouped_matmul
+    import transformer_b200.parts.linear as L
+    x, wgu, wd, idx = _grouped_case(torch.bfloat16, E, k, nt, d, di, seed=31 + E)
+    M = nt * k
+    off = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    st = torch.empty(M, dtype=torch.int32, device="cuda")
+    pr = torch.empty(M, dtype=torch.int32, device="cuda")
+    lib.call("tb_moe_dispatch", idx.data_ptr(), off.data_ptr(), st.data_ptr(), pr.data_ptr(), M, k, E)
+    bufs = {}
+    scratch = lambda name, shape, dt: bufs.setdefault(name, torch.empty(shape, dtype=dt, device="cuda"))
+    old = L.SKINNY_MAX_PAIRS
+    L.SKINNY_MAX_PAIRS = 0          # force the prompt kernel whatever the size
+    try:
+        h = torch.empty((M, di), dtype=torch.bfloat16, device="cuda")
+        y = torch.empty((M, d), dtype=torch.bfloat16, device="cuda")
+        grouped_matmul(x, wgu, h, a_rows=st, group_offsets=off, groups=E, swiglu=True, scratch=scratch)
+        grouped_matmul(h, wd, y, group_offsets=off, groups=E)
+    finally:
+        L.SKINNY_MAX_PAIRS = old
+    assert "grouped.sorted_rows" in bufs, "the tensor-core path was taken"
+    assert lib.gemm_tc_status() == 0
+    prc = pr.cpu()
+    xs, wg, wdd = x.double().cpu(), wgu.double().cpu(), wd.double().cpu()
+    worst = 0.0
+    for t in range(0, nt, max(1, nt // 40)):
+        for j in range(k):
+            e = int(idx[t, j])
+            gu = wg[e] @ xs[t]
+            href = P.silu(gu[:di]) * gu[di:]
+            r = int(prc[t * k + j])
+            assert float((h[r].double().cpu() - href).abs().max()) <= _tol(torch.bfloat16, float(href.abs().max()) + 1e-3)
+            yref = wdd[e] @ h[r].double().cpu()
+            worst = max(worst, float((y[r].double().cpu() - yref).abs().max()) / (float(yref.abs().max()) + 1e-6))
+    assert worst <= 2.0 ** -7

@@ -187,18 +187,20 @@ static int skinny_launch_nt(const SkinnyArgs& a, int out_kind, cudaStream_t s) {
 
 extern "C" {
 // out_kind: 0 = bfloat16 out, 1 = float out, 2 = swiglu pair (bfloat16 out).  M is the number of rows
-// (with group_offsets: an upper bound on the rows of any one group is min(M, rows of that group)).
+// over all groups; max_group_rows bounds the rows of any ONE group (for experts: the number of tokens,
+// since a token picks an expert at most once) and only chooses how many rows a pass takes at once.
 int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
                         long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G, int out_kind,
-                        cudaStream_t s) {
+                        int max_group_rows, cudaStream_t s) {
     if (M < 0 || N <= 0 || K <= 0 || G <= 0) return TB_ERR_ARG;
     if (K % 8 || ldx % 8 || ldw % 8 || (w_group_stride % 8)) return TB_ERR_UNSUPPORTED;
     if (((uintptr_t)X | (uintptr_t)W) & 15) return TB_ERR_UNSUPPORTED;
     if (M == 0) return 0;
     SkinnyArgs a{(const __nv_bfloat16*)X, x_rows, (const __nv_bfloat16*)W, Y, group_offsets, w_group_stride,
                  ldx, ldw, ldy, M, N, K, G};
-    if (M <= 8) return skinny_launch_nt<1>(a, out_kind, s);
-    if (M <= 16) return skinny_launch_nt<2>(a, out_kind, s);
+    const int rows = (max_group_rows > 0 && max_group_rows < M) ? max_group_rows : M;
+    if (rows <= 8) return skinny_launch_nt<1>(a, out_kind, s);
+    if (rows <= 16) return skinny_launch_nt<2>(a, out_kind, s);
     return skinny_launch_nt<4>(a, out_kind, s);
 }
 }

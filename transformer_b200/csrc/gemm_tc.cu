@@ -1,0 +1,402 @@
+// Matrix products for prompts on the 5th-generation tensor cores (tcgen05), bfloat16 in, float
+// accumulation in tensor memory:   C[m, :] = A[m, :] . B[g(m)]^T
+//
+//   * operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), a
+//     ring of TC_STAGES stages of A [128 x 64] and B [256 x 64];
+//   * one elected thread issues tcgen05.mma (M = 128, N = 256, K = 16 per instruction, cta_group::1);
+//     the accumulator [128 x 256] float lives in TMEM (256 columns);
+//   * tcgen05.commit hands a finished stage back to the TMA warp and, after the last k-block,
+//     the accumulator to the four epilogue warps, which read it with tcgen05.ld, apply the
+//     epilogue in float and store.
+//   Warp roles: 0 = TMA producer, 1 = TMEM allocation + MMA issue, 2..5 = epilogue.
+//
+//   * grouped (the experts, models/llama/common/src/compute.rs:319-330 done as one product per
+//     expert over all of its tokens): rows of A are sorted by group; B is the stack of the groups'
+//     matrices viewed as one [G * rows, K] tensor; a block finds its (group, first row) from
+//     group_offsets.  Rows of the tile that belong to the next group are computed and not stored.
+//   * DUAL (swiglu, compute.rs:324-326): the B tile is 128 gate rows followed by the 128 matching
+//     up rows, so one N = 256 instruction yields both; the epilogue stores silu(gate) * up.
+//   * edges: TMA fills out-of-range rows and the K tail with zeros; stores are predicated.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets *error (nonzero), the block
+// stops issuing work, waits (bounded) for its own copies in flight, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BN 256
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_THREADS 192
+#define TC_A_BYTES (TC_BM * TC_BK * 2)
+#define TC_B_BYTES (TC_BN * TC_BK * 2)
+#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
+#define TC_SPIN_LIMIT (1u << 22)
+
+struct TcArgs {
+    void* C;
+    const int* group_offsets;
+    int* error;
+    int ldc, M, N, K, G;
+    int b_group_rows;   // rows of B per group in the stacked view (N, or 2N when dual)
+    int dual;
+    int out_float;
+};
+
+// ---- small PTX wrappers ----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and *error set) when the barrier did not flip in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicCAS(error, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive accumulator columns of this thread's row (lane of TMEM)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile, rows of 64 bfloat16 (128 bytes), 128-byte swizzle
+// as TMA wrote it; groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);   // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N x M.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- the kernel ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                            const __grid_constant__ CUtensorMap map_b,
+                                                            const TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * TC_STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which rows does this block own?
+    int g = 0, row0 = 0, row_end = a.M;
+    bool have_tile = true;
+    if (a.group_offsets) {
+        int tile = blockIdx.x, cum = 0;
+        have_tile = false;
+        for (g = 0; g < a.G; ++g) {
+            const int lo = a.group_offsets[g], hi = a.group_offsets[g + 1];
+            const int tiles = (hi - lo + TC_BM - 1) / TC_BM;
+            if (tile < cum + tiles) {
+                row0 = lo + (tile - cum) * TC_BM;
+                row_end = hi;
+                have_tile = true;
+                break;
+            }
+            cum += tiles;
+        }
+    } else {
+        row0 = blockIdx.x * TC_BM;
+        have_tile = row0 < a.M;
+    }
+    if (!have_tile) return;   // the whole block leaves before any barrier or TMEM exists
+    const int n_out = a.dual ? TC_BN / 2 : TC_BN;       // output columns of the tile
+    const int n0 = blockIdx.y * n_out;
+    const int nkb = (a.K + TC_BK - 1) / TC_BK;
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (TC_STAGES + s); };
+    const uint32_t acc_bar = bar0 + 8u * (2 * TC_STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TC_BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const int b_row = g * a.b_group_rows + n0;
+            bool ok = true;
+            int issued = 0;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % TC_STAGES;
+                if (kb >= TC_STAGES) ok = mbar_wait(empty_bar(s), ((kb / TC_STAGES) - 1) & 1, a.error, 1);
+                if (!ok) break;
+                const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                mbar_expect_tx(full_bar(s), TC_STAGE_BYTES);
+                tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, row0);
+                if (a.dual) {
+                    tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, b_row);
+                    tma_load_2d(sb + TC_B_BYTES / 2, &map_b, full_bar(s), kb * TC_BK, b_row + a.N);
+                } else {
+                    tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, b_row);
+                    tma_load_2d(sb + TC_B_BYTES / 2, &map_b, full_bar(s), kb * TC_BK, b_row + TC_BN / 2);
+                }
+                issued = kb + 1;
+            }
+            if (*(volatile int*)a.error != 0) {
+                // something gave up: let this block's own copies land before the block goes away
+                for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb)
+                    mbar_wait(full_bar(kb % TC_STAGES), (kb / TC_STAGES) & 1, a.error, 4);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(TC_BM, TC_BN);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % TC_STAGES;
+                ok = mbar_wait(full_bar(s), (kb / TC_STAGES) & 1, a.error, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                const uint64_t da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along K: +2 in units of 16 bytes
+                    umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                umma_commit(empty_bar(s));             // the stage is free once these MMAs have read it
+            }
+            umma_commit(acc_bar);                      // the accumulator is complete (or abandoned)
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lanes 32 * (warp % 4) ----------------
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int m = row0 + row;
+        const bool ok = mbar_wait(acc_bar, 0, a.error, 3);
+        tc_fence_after();
+        if (ok) {
+            const uint32_t trow = tmem_acc + ((uint32_t)(quad * 32) << 16);
+            for (int c0 = 0; c0 < n_out; c0 += 32) {
+                float v[32];
+                tmem_ld32(trow + c0, v);               // warp-collective: every lane takes part
+                if (a.dual) {
+                    float u[32];
+                    tmem_ld32(trow + TC_BN / 2 + c0, u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                }
+                if (m < row_end && n0 + c0 < a.N) {
+                    if (a.out_float) {
+                        float* dst = static_cast<float*>(a.C) + (size_t)m * a.ldc + n0 + c0;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c0 + i < a.N) dst[i] = v[i];
+                    } else {
+                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.C) + (size_t)m * a.ldc + n0 + c0;
+                        if (n0 + c0 + 32 <= a.N && ((((size_t)m * a.ldc + n0 + c0) & 7) == 0)) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[i], v[i + 1]);
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                                uint4 pk;
+                                pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                                pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                                pk.z = *reinterpret_cast<uint32_t*>(&p2);
+                                pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(dst + i) = pk;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (n0 + c0 + i < a.N) dst[i] = __float2bfloat16_rn(v[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_acc, TC_BN);
+}
+
+// Gather rows: out[m, :] = x[rows[m], :]  (activations sorted by expert, so that TMA can fetch tiles)
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rows,
+                                   __nv_bfloat16* __restrict__ out, int d) {
+    const int m = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)rows[m] * d);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)m * d);
+    for (int c = threadIdx.x; c < d / 8; c += blockDim.x) dst[c] = src[c];
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// [rows, K] bfloat16, row pitch ld elements; box = 64 columns x box_rows rows, 128-byte swizzle.
+static int make_map(CUtensorMap* out, const void* base, long long rows, int K, long long ld, int box_rows) {
+    static std::map<std::tuple<const void*, long long, int, long long, int>, CUtensorMap> cache;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> hold(lock);
+    auto key = std::make_tuple(base, rows, K, ld, box_rows);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return 0;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return TB_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return TB_ERR_ARG;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return 0;
+}
+
+static __device__ int tc_error_word;
+
+extern "C" {
+// C[m] = A[m] . B[g(m)]^T.  A [M, K] (rows sorted by group), B [G, rows_b, K] with rows_b = N (or 2N when
+// out_kind == 2: gate rows then up rows).  out_kind: 0 bfloat16, 1 float, 2 swiglu (bfloat16).
+// Refuses (TB_ERR_UNSUPPORTED) what TMA cannot address: K or a pitch that is no multiple of 8,
+// a base that is not 16-byte aligned.
+int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offsets, int lda, int ldb, int ldc, int M,
+                    int N, int K, int G, int out_kind, cudaStream_t s) {
+    if (M < 0 || N <= 0 || K <= 0 || G <= 0 || out_kind < 0 || out_kind > 2) return TB_ERR_ARG;
+    if (K % 8 || lda % 8 || ldb % 8) return TB_ERR_UNSUPPORTED;
+    if (((uintptr_t)A | (uintptr_t)B) & 15) return TB_ERR_UNSUPPORTED;
+    if (M == 0) return 0;
+    const int dual = out_kind == 2;
+    const int rows_b = dual ? 2 * N : N;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, M, K, lda, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, (long long)G * rows_b, K, ldb, TC_BN / 2);
+    if (rc) return rc;
+    static int* err_ptr = nullptr;
+    static bool configured = false;
+    const size_t smem = (size_t)TC_STAGES * TC_STAGE_BYTES + 1024;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaGetSymbolAddress((void**)&err_ptr, tc_error_word);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1};
+    const int n_out = dual ? TC_BN / 2 : TC_BN;
+    const int tiles_m = group_offsets ? (M + TC_BM - 1) / TC_BM + G : (M + TC_BM - 1) / TC_BM;
+    dim3 grid(tiles_m, (N + n_out - 1) / n_out);
+    gemm_tc_kernel<<<grid, TC_THREADS, smem, s>>>(ma, mb, a);
+    return tb_last_error();
+}
+
+// Nonzero if any tensor-core product gave up on a wait since the last call (1 producer, 2 MMA,
+// 3 epilogue, 4 drain); reading it synchronises the device and clears it.
+int tb_gemm_tc_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, tc_error_word, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(tc_error_word, &zero, sizeof(int));
+    return v;
+}
+
+int tb_gather_rows_bf16(const void* x, const int* rows, void* out, int M, int d, cudaStream_t s) {
+    if (M < 0 || d <= 0) return TB_ERR_ARG;
+    if (d % 8 || (((uintptr_t)x | (uintptr_t)out) & 15)) return TB_ERR_UNSUPPORTED;
+    if (M == 0) return 0;
+    gather_rows_kernel<<<M, 128, 0, s>>>((const __nv_bfloat16*)x, rows, (__nv_bfloat16*)out, d);
+    return tb_last_error();
+}
+}

@@ -81,9 +81,9 @@ class MoE(FeedForward):
                  M, self.k, self.E)
         h = ctx.scratch("moe.h", (M, self.di), self.dtype)
         grouped_matmul(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
-                       swiglu=True)
+                       swiglu=True, max_group_rows=nt, scratch=ctx.scratch)
         y = ctx.scratch("moe.y", (M, self.d), self.dtype)
-        grouped_matmul(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E)
+        grouped_matmul(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E, max_group_rows=nt)
         # the weighted sum over the chosen experts is left to the norm that follows (fused there)
         return WeightedRows(y, pair_row, w, self.k)
 

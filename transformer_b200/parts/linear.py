@@ -28,11 +28,12 @@ def gemm_simt(a, w, out, *, a_rows=None, group_offsets=None, groups=1, rows=None
              lib.ptr(group_offsets), stride, a.stride(0), ldb, out.stride(0), M, N, K, groups, out_kind)
 
 
+DENSE_TC = False           # dense bfloat16 products of many rows: this package's tcgen05 kernel instead of cuBLAS
 SKINNY_MAX_ROWS = 64       # dense: up to this many rows the weight-streaming kernel is used
 SKINNY_MAX_PAIRS = 512     # grouped: up to this many rows over all groups
 
 
-def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kind=0) -> bool:
+def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kind=0, max_group_rows=0) -> bool:
     """The decode kernel (bfloat16, tensor cores, weights streamed once).  False if it refuses the sizes."""
     M, K, N = out.shape[0], a.shape[-1], out.shape[-1]
     if w.dim() == 3:
@@ -41,7 +42,18 @@ def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kin
         stride, ldw = 0, w.stride(0)
     assert a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
     return lib.try_call("tb_gemm_skinny_bf16", lib.ptr(a), lib.ptr(a_rows), lib.ptr(w), lib.ptr(out),
-                        lib.ptr(group_offsets), stride, a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind)
+                        lib.ptr(group_offsets), stride, a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind,
+                        max_group_rows)
+
+
+def gemm_tc(a, w, out, *, group_offsets=None, groups=1, out_kind=0) -> bool:
+    """The prompt kernel (bfloat16, tcgen05 + TMA + TMEM).  Rows of ``a`` are already sorted by group.
+    False if it refuses the sizes."""
+    M, K, N = out.shape[0], a.shape[-1], out.shape[-1]
+    ldw = w.stride(1) if w.dim() == 3 else w.stride(0)
+    assert a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1 and w.is_contiguous()
+    return lib.try_call("tb_gemm_tc_bf16", lib.ptr(a), lib.ptr(w), lib.ptr(out), lib.ptr(group_offsets),
+                        a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind)
 
 
 def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -55,17 +67,34 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         return
     if M <= SKINNY_MAX_ROWS and gemm_skinny(a, w, out, out_kind=1 if to_float else 0):
         return
+    if (to_float or DENSE_TC) and gemm_tc(a, w, out, out_kind=1 if to_float else 0):
+        return
     if to_float:
         gemm_simt(a, w, out, out_kind=1)
     else:
         torch.mm(a, w.t(), out=out)
 
 
-def grouped_matmul(a, w, out, *, a_rows=None, group_offsets=None, groups=1, swiglu=False) -> None:
+def grouped_matmul(a, w, out, *, a_rows=None, group_offsets=None, groups=1, swiglu=False, max_group_rows=0,
+                   scratch=None) -> None:
     """out[m] = a[a_rows[m] or m] . w[g(m)]^T over rows sorted by group; with swiglu, w[g] holds gate rows
-    then up rows and out = silu(gate) * up."""
+    then up rows and out = silu(gate) * up.  max_group_rows: a bound on the rows of one group, if known;
+    scratch(name, shape, dtype): where the prompt kernel may put the gathered rows."""
     kind = 2 if swiglu else 0
     if a.dtype == torch.bfloat16 and out.shape[0] <= SKINNY_MAX_PAIRS and \
-            gemm_skinny(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind):
+            gemm_skinny(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind,
+                        max_group_rows=max_group_rows):
         return
+    if a.dtype == torch.bfloat16 and w.is_contiguous():
+        src = a
+        if a_rows is not None:
+            # TMA fetches tiles of consecutive rows: bring the rows into their sorted order first
+            src = None
+            if scratch is not None:
+                buf = scratch("grouped.sorted_rows", (out.shape[0], a.shape[-1]), a.dtype)
+                if lib.try_call("tb_gather_rows_bf16", lib.ptr(a), lib.ptr(a_rows), lib.ptr(buf), out.shape[0],
+                                a.shape[-1]):
+                    src = buf
+        if src is not None and gemm_tc(src, w, out, group_offsets=group_offsets, groups=groups, out_kind=kind):
+            return
     gemm_simt(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind)
