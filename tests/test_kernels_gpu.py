@@ -372,3 +372,27 @@ def test_gemm_tc_grouped_swiglu_and_down(E, k, nt, d, di):
             yref = wdd[e] @ h[r].double().cpu()
             worst = max(worst, float((y[r].double().cpu() - yref).abs().max()) / (float(yref.abs().max()) + 1e-6))
     assert worst <= 2.0 ** -7
+
+
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 64), (8, 8, 128), (6, 1, 128)])
+def test_attention_prompt_kernel(nh, nkvh, dh):
+    """The tensor-core prompt kernel on a ragged batch: prompts from zero (shorter and longer than a
+    tile, not multiples of 64), a continued prompt whose cache already holds 130 tokens, a single token."""
+    lib = _lib()
+    dtype = torch.bfloat16
+    tq = lib.attention_prefill_tile_tokens()
+    c = attention_case([150, 1, 64, 37, 200], [0, 90, 0, 130, 64], nh, nkvh, dh, dtype, tq, seed=nh + dh)
+    nt = c["nt"]
+    out = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
+    assert lib.try_call("tb_attention_prefill_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
+                        c["vc"].data_ptr(), c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(), c["tile_nq"].data_ptr(),
+                        c["tok_pos"].data_ptr(), c["table"].data_ptr(), c["tiles"], c["max_pages"], nh * dh, nh,
+                        c["nkvh"], dh, 1.0 / math.sqrt(dh))
+    got = out.double().cpu().reshape(nt, nh, dh)
+    # P is rounded to bfloat16 before P.V: allow for that on top of the storage rounding
+    assert float((got - c["ref"]).abs().max()) <= _tol(dtype, 4.0)
+    # a head size it does not take is refused, not computed wrongly
+    assert not lib.try_call("tb_attention_prefill_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
+                            c["vc"].data_ptr(), c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(),
+                            c["tile_nq"].data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(), c["tiles"],
+                            c["max_pages"], nh * 48, nh, c["nkvh"], 48, 1.0)

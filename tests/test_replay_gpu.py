@@ -13,7 +13,8 @@ from tiny import CONFIGS, TraceRun, check_request, make_folder, n_moe_layers, ra
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 11, 17, 40, 65, 97, 128], "B": [1, 9, 30, 64, 70, 100, 200], "dense": [3, 33, 64, 129]}
+LENGTHS = {"A": [5, 11, 17, 40, 65, 97, 128], "B": [1, 9, 30, 64, 70, 100, 200], "dense": [3, 33, 64, 129],
+           "C": [300, 70, 1, 420]}
 
 
 def _k(cfg):

@@ -38,7 +38,15 @@ TINY_DENSE = {
     "num_key_value_heads": 2, "head_dim": 48, "intermediate_size": 72, "max_position_embeddings": 160,
     "vocab_size": 200, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
 }
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 2), "dense": (TINY_DENSE, 5)}
+# A head size and prompt lengths that reach the tensor-core prompt kernels (attention with heads of 64,
+# expert products over more than 512 (token, expert) pairs).
+TINY_C = {
+    "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 88, "num_local_experts": 5,
+    "num_experts_per_tok": 2, "max_position_embeddings": 512, "vocab_size": 320, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0, "tie_word_embeddings": False,
+}
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 2), "dense": (TINY_DENSE, 5), "C": (TINY_C, 7)}
 
 FP32_TOL = 1e-4          # absolute, on logits of order one
 BF16_REL_TOL = 2.0 ** -6  # of the largest |logit| of the request

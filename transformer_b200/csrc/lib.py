@@ -30,13 +30,14 @@ _SIGNATURES: Dict[str, str] = {
     "tb_gemm_simt_f32": "pppppliiiiiiii".replace(" ", ""), "tb_gemm_simt_bf16": "pppppliiiiiiii",
     "tb_gemm_skinny_bf16": "pppppliiiiiiiii",
     "tb_attention_decode_f32": "ppppppppiiiiiiif", "tb_attention_decode_bf16": "ppppppppiiiiiiif",
+    "tb_attention_prefill_bf16": "pppppppppiiiiiif",
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
     "tb_router_f32": "pppppiiii", "tb_router_bf16": "pppppiiii",
     "tb_moe_dispatch": "ppppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
     "tb_sample": "plpiififpp",
 }
-_NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": ""}
+_NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": ""}
 
 _lock = threading.Lock()
 _lib = None
@@ -128,3 +129,7 @@ def gemm_tc_status() -> int:
     """0, or the code of a tensor-core product that gave up on a wait since the last call
     (synchronises the device)."""
     return library().tb_gemm_tc_status()
+
+
+def attention_prefill_tile_tokens() -> int:
+    return library().tb_attention_prefill_tile_tokens()

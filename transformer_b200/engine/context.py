@@ -152,9 +152,9 @@ class StepContext:
     def scratch(self, name: str, shape, dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
 
-    def attention_tiles(self, nh: int, nkvh: int) -> AttentionTiles:
-        from ..csrc import lib
-        tq = lib.attention_tile_tokens(nh, nkvh)
+    def tiles(self, tq: int) -> AttentionTiles:
+        """Each sequence's new tokens cut into tiles of tq tokens (the sizes the model's mixers
+        announced in ``tile_sizes`` are planned with every step)."""
         if tq not in self._tile_counts:
             raise RuntimeError(f"no query tiles of {tq} tokens were planned for this step")
         return AttentionTiles(self._view(f"tile_seq.{tq}"), self._view(f"tile_t0.{tq}"),

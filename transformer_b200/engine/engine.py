@@ -54,8 +54,7 @@ class Engine:
         self.workspace = Workspace(device, on_grow=self._drop_graphs)
         self._identity_tables = {}
         self.recorder = None    # callable(name, run index, tensor copy) for debugging; see StepContext.record
-        self._tile_sizes = sorted({lib.attention_tile_tokens(m.nh, m.nkvh) for m in mixers
-                                   if hasattr(m, "nh") and hasattr(m, "nkvh")})
+        self._tile_sizes = sorted({int(t) for m in mixers for t in getattr(m, "tile_sizes", ())})
         self._staging = []
         self._staging_next = 0
         self._staging_dev = None

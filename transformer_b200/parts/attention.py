@@ -34,7 +34,10 @@ class Attention(Mixer):
         self.position = POSITIONS.build(pos, dtype, device) if isinstance(pos, PartSpec) else None
         self.qkv_width = (self.nh + 2 * self.nkvh) * self.dh
         self.scale = 1.0 / math.sqrt(self.dh)
-        self.tile_tokens = None
+        # query tiles this mixer asks the step to plan: the general kernel's, and the prompt kernel's
+        self.general_tile = lib.attention_tile_tokens(self.nh, self.nkvh)
+        self.prompt_tile = lib.attention_prefill_tile_tokens() if (dtype == torch.bfloat16 and self.dh in (64, 128)) else 0
+        self.tile_sizes = [self.general_tile] + ([self.prompt_tile] if self.prompt_tile else [])
 
     def parameters(self):
         return {
@@ -65,7 +68,15 @@ class Attention(Mixer):
         if ctx.decode and self._decode_kernel(ctx, qkv, o, cache, table, nt, sfx):
             matmul_nt(o, self.weights["wo"], out)
             return
-        tiles = ctx.attention_tiles(self.nh, self.nkvh)
+        if self.prompt_tile and nt >= 2 * ctx.B:
+            tiles = ctx.tiles(self.prompt_tile)
+            if lib.try_call("tb_attention_prefill_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                            lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos),
+                            lib.ptr(table), tiles.count, ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh,
+                            self.scale):
+                matmul_nt(o, self.weights["wo"], out)
+                return
+        tiles = ctx.tiles(self.general_tile)
         splits = ctx.attention_splits(tiles.count, self.nh, self.nkvh)
         partial = None
         if splits > 1:
