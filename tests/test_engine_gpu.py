@@ -1,0 +1,255 @@
+"""The engine through its Python API: long decoding, first tokens, slots used again, steps cut
+into pieces, CUDA-graph steps, errors, and generation through the entry point."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import transformer_b200 as tb
+from plain import llama_moe_plain as P
+from tiny import BF16_REL_TOL, CONFIGS, FP32_TOL, ROOT, check_request, make_folder, n_moe_layers, random_prompts
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("engine_models")
+    return {n: make_folder(tmp, n) for n in CONFIGS}
+
+
+class Recorder:
+    """Collects the experts chosen per run of the model for the steps it watches."""
+
+    def __init__(self, engine):
+        self.engine, self.items = engine, []
+        engine.recorder = self
+
+    def __call__(self, name, run, t):
+        if name == "moe.topk_idx":
+            self.items.append(t.cpu())
+
+    def take(self):
+        out, self.items = self.items, []
+        return out           # [runs] of [nt, k]
+
+
+def _run_and_check(engine, cfg, tensors, dtype, tokens, cuts, label):
+    """Feed ``tokens`` of one request in consecutive pieces of the given lengths and compare every
+    position with the plain implementation."""
+    rec = Recorder(engine)
+    engine.use_graphs = False      # the recorder needs Python to run; graphs are compared separately
+    slot = engine.open()
+    got, routes, pos = {}, {}, 0
+    try:
+        for n in cuts:
+            piece = tokens[pos:pos + n]
+            lg = engine.step([slot], [piece], [list(range(n))]).cpu()
+            r = rec.take()
+            for i in range(n):
+                got[pos + i] = lg[i]
+                if r:
+                    routes[pos + i] = torch.stack([x[i] for x in r])
+            pos += n
+    finally:
+        engine.close(slot)
+        engine.recorder = None
+        engine.use_graphs = True
+    rt = None
+    if n_moe_layers(cfg):
+        rt = torch.stack([routes[p] for p in range(len(tokens))], dim=1).numpy()
+    return check_request(cfg, tensors, tokens, got, rt, dtype, label)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding_to_the_end_of_the_context(name, dtype, folders):
+    cfg, _ = CONFIGS[name]
+    _, tensors = P.read_folder(folders[name])
+    n = cfg["max_position_embeddings"]
+    tokens = random_prompts(cfg["vocab_size"], [n], seed=11)[0]
+    engine = tb.load(folders[name], dtype=dtype, max_tokens=n + 64)
+    _run_and_check(engine, cfg, tensors, dtype, tokens, [5] + [1] * (n - 5), f"long decoding {name}")
+    with pytest.raises(tb.CacheError):       # one token more than the context holds
+        s = engine.open()
+        try:
+            engine.step([s], [tokens])
+            engine.step([s], [[1]])
+        finally:
+            engine.close(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(dtype, folders):
+    cfg, _ = CONFIGS["B"]
+    _, tensors = P.read_folder(folders["B"])
+    engine = tb.load(folders["B"], dtype=dtype, max_tokens=256)
+    for cuts in ([1], [1, 1], [1, 1, 1], [2, 1], [3]):
+        tokens = random_prompts(cfg["vocab_size"], [sum(cuts)], seed=sum(cuts) + len(cuts))[0]
+        _run_and_check(engine, cfg, tensors, dtype, tokens, cuts, f"first tokens {cuts}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_slot_used_again_sees_nothing_of_its_past(dtype, folders):
+    cfg, _ = CONFIGS["A"]
+    _, tensors = P.read_folder(folders["A"])
+    engine = tb.load(folders["A"], dtype=dtype, max_tokens=128, max_slots=1)   # one slot, two pages: all reuse
+    long, short = random_prompts(cfg["vocab_size"], [128, 40], seed=5)
+    _run_and_check(engine, cfg, tensors, dtype, long, [100] + [1] * 28, "first tenant")
+    _run_and_check(engine, cfg, tensors, dtype, short, [7, 20] + [1] * 13, "second tenant of the same slot and pages")
+    engine.cache.table.check()
+    assert engine.cache.table.pages.free == 2 and engine.cache.table.slots.free == 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_step_cut_into_pieces_changes_nothing(dtype, folders):
+    cfg, _ = CONFIGS["C"]
+    _, tensors = P.read_folder(folders["C"])
+    prompts = random_prompts(cfg["vocab_size"], [90, 33, 150], seed=8)
+    whole = tb.load(folders["C"], dtype=dtype, max_tokens=512)
+    pieces = tb.load(folders["C"], dtype=dtype, max_tokens=512, max_step_tokens=64)   # 273 tokens: 5 pieces
+    outs = []
+    for eng in (whole, pieces):
+        slots = [eng.open() for _ in prompts]
+        want = [[0, len(p) // 2, len(p) - 1] for p in prompts]
+        outs.append(eng.step(slots, prompts, want).cpu())
+        outs.append(eng.step(slots, [[3], [4], [5]]).cpu())
+    tol = 1e-5 if dtype == "float32" else BF16_REL_TOL * float(outs[0].abs().max())
+    assert float((outs[0] - outs[2]).abs().max()) <= tol
+    assert float((outs[1] - outs[3]).abs().max()) <= tol
+    ref = torch.stack([P.forward(cfg, tensors, p, want=[0, len(p) // 2, len(p) - 1]) for p in prompts]).reshape(9, -1)
+    if dtype == "float32":
+        assert float((outs[2] - ref).abs().max()) <= FP32_TOL
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_steps_equal_eager_steps(dtype, folders):
+    """Decode steps replay a CUDA graph from their third use on; the logits must not change by a bit,
+    for a batch that shrinks and across a page boundary."""
+    cfg, _ = CONFIGS["B"]
+    prompts = random_prompts(cfg["vocab_size"], [60, 62, 3], seed=9)
+    feeds = random_prompts(cfg["vocab_size"], [10, 10, 10], seed=10)
+    results = []
+    for graphs in (False, True):
+        eng = tb.load(folders["B"], dtype=dtype, max_tokens=512)
+        eng.use_graphs = graphs
+        slots = [eng.open() for _ in prompts]
+        eng.step(slots, prompts)
+        outs = []
+        for j in range(10):
+            live = slots if j < 6 else slots[:2]              # the third sequence ends earlier
+            outs.append(eng.step(live, [[feeds[i][j]] for i in range(len(live))]).cpu().clone())
+        results.append(outs)
+        assert bool(eng._graphs) == graphs
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+
+
+def test_step_refuses_bad_input_and_changes_nothing(folders):
+    eng = tb.load(folders["A"], dtype="float32", max_tokens=128)
+    s = eng.open()
+    for bad in (lambda: eng.step([s], [[256]]), lambda: eng.step([s], [[-1]]), lambda: eng.step([s], [[]]),
+                lambda: eng.step([s], [[1, 2]], [[2]]), lambda: eng.step([s, s], [[1], [2]]),
+                lambda: eng.step([s], [[1], [2]])):
+        with pytest.raises(tb.StepError):
+            bad()
+    with pytest.raises(tb.CacheError):
+        eng.step([s], [[1] * 129])                 # beyond the context
+    s2 = eng.open()
+    eng.step([s], [[1] * 100])
+    with pytest.raises(tb.CacheError, match="cache full"):
+        eng.step([s2], [[1] * 10])                 # 128 tokens of cache: two pages, both taken
+    assert eng.cache.length(s) == 100 and eng.cache.length(s2) == 0
+    eng.cache.table.check()
+    with pytest.raises(tb.CacheError):
+        eng.close(99)
+
+
+# ---------------------------------------------------------------------------------------------
+def _plain_follow(cfg, tensors, prompt, got, dtype, args=None, us=None):
+    """Check generated tokens against the plain implementation, teacher-forced on the engine's own
+    tokens: greedy -> the token's plain logit is the maximum, up to the rounding rule of the path;
+    sampled -> the token is the one whose interval of the plain distribution holds u."""
+    seq = list(prompt)
+    for j, tok in enumerate(got):
+        logits = P.forward(cfg, tensors, seq, want=[len(seq) - 1])[0]
+        if args is None or args.greedy:
+            slack = 2 * (FP32_TOL if dtype == "float32" else BF16_REL_TOL * float(logits.abs().max()))
+            assert float(logits[tok]) >= float(logits.max()) - slack, f"token {j}: {tok} is not the plain argmax"
+        else:
+            kept, probs = P.sample_distribution(logits, args.temperature, args.top_k, args.top_p)
+            assert tok in kept
+            lo = sum(probs[:kept.index(tok)])
+            eps = 1e-3 if dtype == "float32" else 5e-2
+            assert lo - eps <= us[j] <= lo + probs[kept.index(tok)] + eps, f"token {j}: u = {us[j]} misses {tok}"
+        seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "dense"])
+def test_greedy_generation_through_the_entry_point(name, dtype, folders):
+    cfg, _ = CONFIGS[name]
+    _, tensors = P.read_folder(folders[name])
+    prompts = random_prompts(cfg["vocab_size"], [5, 11, 17, 1, 30], seed=1)
+    engine = tb.load(folders[name], dtype=dtype, max_tokens=256)
+    res = tb.generate(engine, prompts, max_steps=8, stop_tokens=(), max_batch=3)     # two batches, slots reused
+    assert res.batches == [[0, 1, 2], [3, 4]] and all(len(t) == 8 for t in res.tokens)
+    for p, got in zip(prompts, res.tokens):
+        _plain_follow(cfg, tensors, p, got, dtype)
+    if dtype == "float32":
+        assert res.tokens == [P.greedy_generate(cfg, tensors, p, 8) for p in prompts]
+    assert engine.cache.table.slots.held == 0 and engine.cache.table.pages.held == 0
+
+
+def test_stop_tokens_end_a_sequence_early(folders):
+    cfg, _ = CONFIGS["A"]
+    _, tensors = P.read_folder(folders["A"])
+    prompts = random_prompts(cfg["vocab_size"], [5, 11, 17], seed=1)
+    engine = tb.load(folders["A"], dtype="float32", max_tokens=256)
+    free = tb.generate(engine, prompts, max_steps=8, stop_tokens=()).tokens
+    stop = free[1][3]                                   # the 4th token of the second request
+    res = tb.generate(engine, prompts, max_steps=8, stop_tokens=[stop])
+    for f, g, why in zip(free, res.tokens, res.finished):
+        cut = f.index(stop) if stop in f else len(f)
+        assert g == f[:cut] and why == ("stop" if stop in f else "length")
+    assert res.finished[1] == "stop" and len(res.tokens[1]) <= 3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_published_workloads(dtype, tmp_path):
+    """The two tiny workloads as stated (weights N(0, 0.02)): A: prompts 5/11/17, 8 greedy steps;
+    B: prompts 1/9/30/64, 12 steps at temperature 0.8 with sampler seed 4."""
+    from transformer_b200.sampling import uniform
+    fa, fb = make_folder(tmp_path, "A", std=0.02), make_folder(tmp_path, "B", std=0.02)
+    (ca, _), (cb, _) = CONFIGS["A"], CONFIGS["B"]
+    _, ta = P.read_folder(fa)
+    _, tb_ = P.read_folder(fb)
+    ea = tb.load(fa, dtype=dtype, max_tokens=256)
+    pa = random_prompts(ca["vocab_size"], [5, 11, 17], seed=1)
+    for p, got in zip(pa, tb.generate(ea, pa, max_steps=8, stop_tokens=()).tokens):
+        _plain_follow(ca, ta, p, got, dtype)
+    eb = tb.load(fb, dtype=dtype, max_tokens=512)
+    pb = random_prompts(cb["vocab_size"], [1, 9, 30, 64], seed=3)
+    args = tb.SampleArgs(temperature=0.8)
+    together = tb.generate(eb, pb, max_steps=12, sample_args=args, seed=4, stop_tokens=()).tokens
+    for r, (p, got) in enumerate(zip(pb, together)):
+        _plain_follow(cb, tb_, p, got, dtype, args, [uniform(4, r, j) for j in range(12)])
+    assert together == tb.generate(eb, pb, max_steps=12, sample_args=args, seed=4, stop_tokens=()).tokens, "repeatable"
+    assert together != tb.generate(eb, pb, max_steps=12, sample_args=args, seed=5, stop_tokens=()).tokens
+
+
+def test_command_line(folders):
+    env = dict(os.environ, TEST_MODEL=folders["A"], TEMPERATURE="0", MAX_STEPS="5", PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "transformer_b200", "generate", "--prompt", "7 8 9", "--prompt",
+                          "1,2", "--dtype", "float32", "--json"], env=env, capture_output=True, text=True, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    got = json.loads(out.stdout.strip().splitlines()[-1])
+    cfg, tensors = P.read_folder(folders["A"])
+    assert got["tokens"] == [P.greedy_generate(cfg, tensors, p, 5) for p in ([7, 8, 9], [1, 2])]
+    out = subprocess.run([sys.executable, "-m", "transformer_b200", "inspect", "--model", folders["B"]],
+                         env=env, capture_output=True, text=True, cwd=ROOT)
+    assert out.returncode == 0 and "nexp=6" in out.stdout and "architecture: llama" in out.stdout
