@@ -81,6 +81,53 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
     for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] *= inv;
 }
 
+// Top-k and weights from router logits that are already in memory (float [nt, E]): one warp per token.
+// Same rules as router_kernel; used when the logits come from a matrix-product kernel.
+__global__ void __launch_bounds__(128)
+topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx, float* __restrict__ topk_w, int nt,
+                    int E, int k) {
+    extern __shared__ float lg_all[];   // [4][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= nt) return;
+    float* lg = lg_all + warp * E;
+    for (int e = lane; e < E; e += 32) lg[e] = logits[(size_t)t * E + e];
+    __syncwarp();
+    float v0 = 0.f, sum = 0.f;
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = lg[e];
+            if (v > best) {
+                best = v;
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (bi >= E) bi = 0;
+        if (j == 0) v0 = best;
+        const float p = expf(best - v0);
+        sum += p;
+        if (lane == 0) {
+            topk_idx[(size_t)t * k + j] = bi;
+            topk_w[(size_t)t * k + j] = p;
+            lg[bi] = __int_as_float(0x7fc00000);
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / sum;
+    for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] *= inv;
+}
+
 // One block builds the dispatch lists for M = nt * k (token, choice) pairs:
 //   group_offsets[e] .. group_offsets[e+1]   rows of expert e in the sorted order
 //   sorted_token[r]                          token whose activation row r reads
@@ -157,6 +204,13 @@ int tb_router_f32(const void* x1, const void* wr, int* topk_idx, float* topk_w, 
 int tb_router_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt, int d,
                    int E, int k, cudaStream_t s) {
     return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k, s);
+}
+int tb_topk_softmax(const float* logits, int* topk_idx, float* topk_w, int nt, int E, int k, cudaStream_t s) {
+    if (nt < 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
+    if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
+    if (nt == 0) return 0;
+    topk_softmax_kernel<<<(nt + 3) / 4, 128, (size_t)4 * E * sizeof(float), s>>>(logits, topk_idx, topk_w, nt, E, k);
+    return tb_last_error();
 }
 int tb_moe_dispatch(const int* topk_idx, int* group_offsets, int* sorted_token, int* pair_row, int M, int k, int E,
                     cudaStream_t s) {

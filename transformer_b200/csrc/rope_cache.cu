@@ -60,6 +60,75 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ t
     }
 }
 
+// The same with 8 values per thread and 16-byte accesses (head sizes that are a multiple of 16).
+template <typename T>
+__global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict__ tok_seq,
+                                      const int* __restrict__ tok_pos, const int* __restrict__ page_table,
+                                      int max_pages, const float* __restrict__ cos_t,
+                                      const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
+                                      int nh, int nkvh, int dh, int half_pairing) {
+    const int t = blockIdx.x;
+    const int head_lo = blockIdx.y * ROPE_HEADS;
+    const int head_hi = min(head_lo + ROPE_HEADS, nh + 2 * nkvh);
+    const int pos = tok_pos[t];
+    const int half = dh >> 1;
+    T* row = qkv + (size_t)t * (nh + 2 * nkvh) * dh;
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+    size_t cache_row = 0;
+    if (kc) {
+        const int page = page_table[(size_t)tok_seq[t] * max_pages + pos / TB_PAGE];
+        cache_row = ((size_t)page * nkvh * TB_PAGE + (pos % TB_PAGE)) * dh;
+    }
+    const int rot_hi = min(head_hi, nh + nkvh);
+    const int units = dh / 16;                 // work items per head: 16 values = 8 pairs each
+    for (int idx = threadIdx.x; idx < (rot_hi - head_lo) * units; idx += blockDim.x) {
+        const int head = head_lo + idx / units, u = idx % units;
+        T* h = row + (size_t)head * dh;
+        T* dst = head < nh ? h : (kc ? kc + cache_row + (size_t)(head - nh) * TB_PAGE * dh : nullptr);
+        float a[8], b[8], c[8], s[8], ya[8], yb[8];
+        load8(cs + u * 8, c);                  // pairs 8u .. 8u+7
+        load8(sn + u * 8, s);
+        if (half_pairing) {                    // pair i = (x[i], x[i + half])
+            load8(h + u * 8, a);
+            load8(h + half + u * 8, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                ya[e] = a[e] * c[e] - b[e] * s[e];
+                yb[e] = a[e] * s[e] + b[e] * c[e];
+            }
+            if (dst) {
+                store8(dst + u * 8, ya);
+                store8(dst + half + u * 8, yb);
+            }
+        } else {                               // pair i = (x[2i], x[2i+1]): 16 consecutive values
+            load8(h + u * 16, a);
+            load8(h + u * 16 + 8, b);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                ya[2 * e] = a[2 * e] * c[e] - a[2 * e + 1] * s[e];
+                ya[2 * e + 1] = a[2 * e] * s[e] + a[2 * e + 1] * c[e];
+                yb[2 * e] = b[2 * e] * c[4 + e] - b[2 * e + 1] * s[4 + e];
+                yb[2 * e + 1] = b[2 * e] * s[4 + e] + b[2 * e + 1] * c[4 + e];
+            }
+            if (dst) {
+                store8(dst + u * 16, ya);
+                store8(dst + u * 16 + 8, yb);
+            }
+        }
+    }
+    if (vc && head_hi > nh + nkvh) {
+        const int v_lo = max(head_lo, nh + nkvh);
+        const int per = dh / 8;
+        for (int idx = threadIdx.x; idx < (head_hi - v_lo) * per; idx += blockDim.x) {
+            const int head = v_lo + idx / per, c8 = (idx % per) * 8;
+            float f[8];
+            load8(row + (size_t)head * dh + c8, f);
+            store8(vc + cache_row + (size_t)(head - nh - nkvh) * TB_PAGE * dh + c8, f);
+        }
+    }
+}
+
 template <typename T>
 static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, const int* page_table,
                              int max_pages, const float* cos_t, const float* sin_t, void* kc, void* vc,
@@ -68,6 +137,11 @@ static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, 
     if ((kc == nullptr) != (vc == nullptr)) return TB_ERR_ARG;
     if (nt == 0) return 0;
     dim3 grid(nt, (nh + 2 * nkvh + ROPE_HEADS - 1) / ROPE_HEADS);
+    if (dh % 16 == 0 && (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc) & 15) == 0) {
+        rope_cache_vec_kernel<T><<<grid, 64, 0, s>>>((T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
+                                                     (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
+        return tb_last_error();
+    }
     rope_cache_kernel<T><<<grid, 128, 0, s>>>((T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
                                             (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
     return tb_last_error();

@@ -11,7 +11,9 @@ import torch
 
 from ..csrc import lib
 from .base import FEED_FORWARDS, FeedForward, ParamDecl, WeightedRows
-from .linear import grouped_matmul, matmul_nt
+from .linear import gemm_tc, grouped_matmul, matmul_nt
+
+ROUTER_PRODUCT_ROWS = 256   # above this many tokens the router logits come from the prompt product kernel
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -64,6 +66,13 @@ class MoE(FeedForward):
         nt = x1.shape[0]
         idx = ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32)
         w = ctx.scratch("moe.topk_w", (nt, self.k), torch.float32)
+        if self.dtype == torch.bfloat16 and nt > ROUTER_PRODUCT_ROWS:
+            # many tokens: the logits are a matrix product (tensor cores, float accumulation and output),
+            # then one small kernel picks the experts
+            lg = logits_out if logits_out is not None else ctx.scratch("moe.logits", (nt, self.E), torch.float32)
+            if gemm_tc(x1, self.weights["router"], lg, out_kind=1):
+                lib.call("tb_topk_softmax", lib.ptr(lg), lib.ptr(idx), lib.ptr(w), nt, self.E, self.k)
+                return idx, w
         lib.call("tb_router_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
                  lib.ptr(idx), lib.ptr(w), lib.ptr(logits_out), nt, self.d, self.E, self.k)
         return idx, w
