@@ -37,6 +37,7 @@ struct DecodeArgs {
 
 template <typename T, int GC>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(const DecodeArgs a) {
+    pdl_sync();
     constexpr int EPL = Vec16<T>::N;
     extern __shared__ __align__(16) float sm[];
     const int dh = a.dh;
@@ -207,7 +208,7 @@ static int decode_launch_gc(const DecodeArgs& a, int nt, cudaStream_t s) {
     }
     const int group = a.nh / a.nkvh;
     dim3 grid(nt, a.nkvh * ((group + GC - 1) / GC), a.splits);
-    attention_decode_kernel<T, GC><<<grid, AD_THREADS, smem, s>>>(a);
+    TB_LAUNCH((attention_decode_kernel<T, GC>), grid, AD_THREADS, smem, s, a);
     return tb_last_error();
 }
 
@@ -232,7 +233,7 @@ static int decode_launch(const DecodeArgs& a, int nt, cudaStream_t s) {
     if (rc) return rc;
     if (a.splits > 1) {
         dim3 grid(nt, a.nh);
-        attention_merge_kernel<T><<<grid, a.dh < 128 ? 64 : 128, 0, s>>>(a.partial, (T*)a.out, a.nh, a.dh, a.splits);
+        TB_LAUNCH((attention_merge_kernel<T>), grid, a.dh < 128 ? 64 : 128, 0, s, a.partial, (T*)a.out, a.nh, a.dh, a.splits);
         rc = tb_last_error();
     }
     return rc;

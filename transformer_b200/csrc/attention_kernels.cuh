@@ -42,6 +42,7 @@ struct AttnArgs {
 
 template <typename T, int DPL>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_kernel(const AttnArgs a) {
+    pdl_sync();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int dh = a.dh;
     const int kstride = dh + (sizeof(T) == 4 ? 1 : 2);   // odd word stride: lanes hit distinct banks
@@ -158,6 +159,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_kernel(const AttnArg
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int nh, int dh,
                                        int splits) {
+    pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const float* p = partial + ((size_t)t * nh + h) * splits * (dh + 2);
     float m = -INFINITY;
@@ -195,7 +197,7 @@ static int attention_launch_dpl(const AttnArgs& a, int tiles, cudaStream_t s) {
     const int group = a.nh / a.nkvh;
     const int chunks = (group + a.hc - 1) / a.hc;
     dim3 grid(tiles, a.nkvh * chunks, a.splits);
-    attention_kernel<T, DPL><<<grid, ATT_WARPS * 32, smem, s>>>(a);
+    TB_LAUNCH((attention_kernel<T, DPL>), grid, ATT_WARPS * 32, smem, s, a);
     return tb_last_error();
 }
 
@@ -221,7 +223,7 @@ static int attention_launch(AttnArgs a, int tiles, int nt, cudaStream_t s) {
     if (rc) return rc;
     if (a.splits > 1) {
         dim3 grid(nt, a.nh);
-        attention_merge_kernel<T><<<grid, a.dh < 128 ? 64 : 128, 0, s>>>(a.partial, (T*)a.out, a.nh, a.dh, a.splits);
+        TB_LAUNCH((attention_merge_kernel<T>), grid, a.dh < 128 ? 64 : 128, 0, s, a.partial, (T*)a.out, a.nh, a.dh, a.splits);
         rc = tb_last_error();
     }
     return rc;

@@ -63,6 +63,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 template <int DH>
 __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(const PrefillArgs a) {
+    pdl_sync();
     constexpr int CH = DH / 8;                 // 16-byte chunks in a row
     constexpr int TILE = AP_BN * DH;           // elements of one K or V tile
     extern __shared__ __align__(128) __nv_bfloat16 sm[];
@@ -246,7 +247,7 @@ static int prefill_launch(const PrefillArgs& a, cudaStream_t s) {
         configured = true;
     }
     dim3 grid(a.tiles, a.nh);
-    attention_prefill_kernel<DH><<<grid, AP_THREADS, smem, s>>>(a);
+    TB_LAUNCH((attention_prefill_kernel<DH>), grid, AP_THREADS, smem, s, a);
     return tb_last_error();
 }
 

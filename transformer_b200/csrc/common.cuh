@@ -119,4 +119,32 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
     *reinterpret_cast<uint4*>(p) = v;
 }
 
+// ---- launches with programmatic dependent launch ------------------------------------------------
+// Every kernel of this package begins with pdl_sync(): it lets the next kernel in the stream start
+// launching (its blocks become resident and wait), then waits until the previous kernel has finished
+// and its writes are visible.  Nothing is read or written before that wait, so the overlap never
+// changes a result; what it removes is the launch gap between the many small kernels of a decode step.
+__device__ __forceinline__ void pdl_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static inline void tb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface through cudaGetLastError
+}
+#define TB_LAUNCH(kernel, grid, block, smem, stream, ...) \
+    tb_launch_pdl(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+
 static inline int tb_last_error() { return (int)cudaGetLastError(); }

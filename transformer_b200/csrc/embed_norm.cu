@@ -7,6 +7,7 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ x, int d) {
+    pdl_sync();
     const int i = blockIdx.x;
     const T* src = table + (size_t)tokens[i] * d;
     float* dst = x + (size_t)i * d;
@@ -28,6 +29,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
                                    const float* __restrict__ topk_w, int k,
                                    const int* __restrict__ rows, const float* __restrict__ w,
                                    float eps, T* __restrict__ y, int d) {
+    pdl_sync();
     __shared__ float red[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -69,6 +71,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
                        const int* __restrict__ pair_row, const float* __restrict__ topk_w, int k,
                        const int* __restrict__ rows, const float* __restrict__ w, float eps, T* __restrict__ y,
                        int d) {
+    pdl_sync();
     __shared__ float red[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -124,6 +127,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
 template <typename T>
 __global__ void embed_vec_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ x,
                                  int d) {
+    pdl_sync();
     const int i = blockIdx.x;
     const T* src = table + (size_t)tokens[i] * d;
     float* dst = x + (size_t)i * d;
@@ -139,9 +143,9 @@ static int embed_launch(const int* tokens, const void* table, float* x, int nt, 
     if (nt < 0 || d <= 0) return TB_ERR_ARG;
     if (nt == 0) return 0;
     if (d % 8 == 0)
-        embed_vec_kernel<T><<<nt, 128, 0, s>>>(tokens, (const T*)table, x, d);
+        TB_LAUNCH((embed_vec_kernel<T>), nt, 128, 0, s, tokens, (const T*)table, x, d);
     else
-        embed_kernel<T><<<nt, 256, 0, s>>>(tokens, (const T*)table, x, d);
+        TB_LAUNCH((embed_kernel<T>), nt, 256, 0, s, tokens, (const T*)table, x, d);
     return tb_last_error();
 }
 template <typename T>
@@ -152,12 +156,12 @@ static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const
     if (wy && (delta || !pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
     if (n_out == 0) return 0;
     if (d % 8 == 0 && d <= NORM_THREADS * 8 * NORM_CHUNKS) {
-        add_rmsnorm_vec_kernel<T><<<n_out, NORM_THREADS, 0, s>>>(x, (const T*)delta, (const T*)wy, pair_row, topk_w, k,
+        TB_LAUNCH((add_rmsnorm_vec_kernel<T>), n_out, NORM_THREADS, 0, s, x, (const T*)delta, (const T*)wy, pair_row, topk_w, k,
                                                                 rows, w, eps, (T*)y, d);
         return tb_last_error();
     }
     int threads = d >= 2048 ? 512 : 256;
-    add_rmsnorm_kernel<T><<<n_out, threads, 0, s>>>(x, (const T*)delta, (const T*)wy, pair_row, topk_w, k, rows, w, eps,
+    TB_LAUNCH((add_rmsnorm_kernel<T>), n_out, threads, 0, s, x, (const T*)delta, (const T*)wy, pair_row, topk_w, k, rows, w, eps,
                                                    (T*)y, d);
     return tb_last_error();
 }

@@ -30,6 +30,7 @@ struct GemmArgs {
 
 template <typename T, typename TC, int BM, bool DUAL>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmArgs a) {
+    pdl_sync();
     constexpr int TM = BM / 16;
     __shared__ float As[GB_K][BM + 1];
     __shared__ float Bs[GB_K][GB_N + 1];
@@ -146,9 +147,9 @@ static int gemm_simt_launch(const GemmArgs& a, cudaStream_t s) {
     const int tiles = a.group_offsets ? (a.M + bm - 1) / bm + a.G : (a.M + bm - 1) / bm;
     dim3 grid(tiles, (a.N + GB_N - 1) / GB_N);
     if (small)
-        gemm_simt_kernel<T, TC, 16, DUAL><<<grid, 256, 0, s>>>(a);
+        TB_LAUNCH((gemm_simt_kernel<T, TC, 16, DUAL>), grid, 256, 0, s, a);
     else
-        gemm_simt_kernel<T, TC, 64, DUAL><<<grid, 256, 0, s>>>(a);
+        TB_LAUNCH((gemm_simt_kernel<T, TC, 64, DUAL>), grid, 256, 0, s, a);
     return tb_last_error();
 }
 

@@ -56,6 +56,7 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
 // 16-byte loads in flight (the step is bound by memory latency x bytes in flight otherwise).
 template <int NT, bool DUAL, typename TY, int WK, int WN, int UNR>
 __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyArgs a) {
+    pdl_sync();
     constexpr int ROWS = 8 * NT;
     constexpr int NMAT = DUAL ? 2 : 1;
     __shared__ float red[WN][WK][NMAT][ROWS][SK_COLS + 1];
@@ -168,11 +169,11 @@ static int skinny_launch_shape(const SkinnyArgs& a, cudaStream_t s) {
     if (a.K >= 2048) {
         constexpr int WK = 8, WN = 1, UNR = NT >= 4 ? 2 : 4;
         dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
-        gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR><<<grid, WK * WN * 32, 0, s>>>(a);
+        TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR>), grid, WK * WN * 32, 0, s, a);
     } else {
         constexpr int WK = 2, WN = 4, UNR = NT >= 4 ? 2 : 4;
         dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
-        gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR><<<grid, WK * WN * 32, 0, s>>>(a);
+        TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR>), grid, WK * WN * 32, 0, s, a);
     }
     return tb_last_error();
 }

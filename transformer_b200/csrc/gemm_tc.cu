@@ -139,6 +139,7 @@ __device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                             const __grid_constant__ CUtensorMap map_b,
                                                             const TcArgs a) {
+    pdl_sync();
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * TC_STAGES + 1];
     __shared__ uint32_t tmem_slot;
@@ -295,6 +296,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 // Gather rows: out[m, :] = x[rows[m], :]  (activations sorted by expert, so that TMA can fetch tiles)
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rows,
                                    __nv_bfloat16* __restrict__ out, int d) {
+    pdl_sync();
     const int m = blockIdx.x;
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)rows[m] * d);
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)m * d);
@@ -379,7 +381,7 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     const int n_out = dual ? TC_BN / 2 : TC_BN;
     const int tiles_m = group_offsets ? (M + TC_BM - 1) / TC_BM + G : (M + TC_BM - 1) / TC_BM;
     dim3 grid(tiles_m, (N + n_out - 1) / n_out);
-    gemm_tc_kernel<<<grid, TC_THREADS, smem, s>>>(ma, mb, a);
+    TB_LAUNCH((gemm_tc_kernel), grid, TC_THREADS, smem, s, ma, mb, a);
     return tb_last_error();
 }
 
@@ -396,7 +398,7 @@ int tb_gather_rows_bf16(const void* x, const int* rows, void* out, int M, int d,
     if (M < 0 || d <= 0) return TB_ERR_ARG;
     if (d % 8 || (((uintptr_t)x | (uintptr_t)out) & 15)) return TB_ERR_UNSUPPORTED;
     if (M == 0) return 0;
-    gather_rows_kernel<<<M, 128, 0, s>>>((const __nv_bfloat16*)x, rows, (__nv_bfloat16*)out, d);
+    TB_LAUNCH((gather_rows_kernel), M, 128, 0, s, (const __nv_bfloat16*)x, rows, (__nv_bfloat16*)out, d);
     return tb_last_error();
 }
 }

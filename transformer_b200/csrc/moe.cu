@@ -18,6 +18,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restrict__ topk_idx,
               float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d, int E, int k) {
+    pdl_sync();
     constexpr int EPL = Vec16<T>::N;
     extern __shared__ float lg[];   // [E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -86,6 +87,7 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
 __global__ void __launch_bounds__(128)
 topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx, float* __restrict__ topk_w, int nt,
                     int E, int k) {
+    pdl_sync();
     extern __shared__ float lg_all[];   // [4][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 4 + warp;
@@ -137,6 +139,7 @@ topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx
 __global__ void __launch_bounds__(1024)
 moe_dispatch_kernel(const int* __restrict__ topk_idx, int* __restrict__ group_offsets,
                     int* __restrict__ sorted_token, int* __restrict__ pair_row, int M, int k, int E) {
+    pdl_sync();
     __shared__ int count[ROUTER_MAX_E + 1];
     __shared__ int cursor[ROUTER_MAX_E];
     for (int e = threadIdx.x; e <= E; e += blockDim.x) count[e] = 0;
@@ -166,6 +169,7 @@ moe_dispatch_kernel(const int* __restrict__ topk_idx, int* __restrict__ group_of
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ pair_row,
                                    const float* __restrict__ topk_w, T* __restrict__ delta, int d, int k) {
+    pdl_sync();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float acc = 0.f;
@@ -183,7 +187,7 @@ static int router_launch(const void* x1, const void* wr, int* topk_idx, float* t
     if (nt == 0) return 0;
     int warps = E < ROUTER_WARPS ? E : ROUTER_WARPS;
     if (nt >= 1024 && warps > 4) warps = 4;   // many tokens: fewer, longer-lived warps per token
-    router_kernel<T><<<nt, warps * 32, (size_t)E * sizeof(float), s>>>(
+    TB_LAUNCH((router_kernel<T>), nt, warps * 32, (size_t)E * sizeof(float), s, 
         (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k);
     return tb_last_error();
 }
@@ -192,7 +196,7 @@ static int combine_launch(const void* y, const int* pair_row, const float* topk_
                           int k, cudaStream_t s) {
     if (nt < 0 || d <= 0 || k <= 0) return TB_ERR_ARG;
     if (nt == 0) return 0;
-    moe_combine_kernel<T><<<nt, 256, 0, s>>>((const T*)y, pair_row, topk_w, (T*)delta, d, k);
+    TB_LAUNCH((moe_combine_kernel<T>), nt, 256, 0, s, (const T*)y, pair_row, topk_w, (T*)delta, d, k);
     return tb_last_error();
 }
 
@@ -209,14 +213,14 @@ int tb_topk_softmax(const float* logits, int* topk_idx, float* topk_w, int nt, i
     if (nt < 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
     if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
-    topk_softmax_kernel<<<(nt + 3) / 4, 128, (size_t)4 * E * sizeof(float), s>>>(logits, topk_idx, topk_w, nt, E, k);
+    TB_LAUNCH((topk_softmax_kernel), (nt + 3) / 4, 128, (size_t)4 * E * sizeof(float), s, logits, topk_idx, topk_w, nt, E, k);
     return tb_last_error();
 }
 int tb_moe_dispatch(const int* topk_idx, int* group_offsets, int* sorted_token, int* pair_row, int M, int k, int E,
                     cudaStream_t s) {
     if (M < 0 || k <= 0 || E <= 0) return TB_ERR_ARG;
     if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
-    moe_dispatch_kernel<<<1, 1024, 0, s>>>(topk_idx, group_offsets, sorted_token, pair_row, M, k, E);
+    TB_LAUNCH((moe_dispatch_kernel), 1, 1024, 0, s, topk_idx, group_offsets, sorted_token, pair_row, M, k, E);
     return tb_last_error();
 }
 int tb_moe_combine_f32(const void* y, const int* pair_row, const float* topk_w, void* delta, int nt, int d, int k,

@@ -18,6 +18,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ t
                                   int max_pages, const float* __restrict__ cos_t,
                                   const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
                                   int nh, int nkvh, int dh, int half_pairing) {
+    pdl_sync();
     // grid: (token, chunk of ROPE_HEADS heads out of q heads, k heads, v heads in that order)
     const int t = blockIdx.x;
     const int head_lo = blockIdx.y * ROPE_HEADS;
@@ -67,6 +68,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict
                                       int max_pages, const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
                                       int nh, int nkvh, int dh, int half_pairing) {
+    pdl_sync();
     const int t = blockIdx.x;
     const int head_lo = blockIdx.y * ROPE_HEADS;
     const int head_hi = min(head_lo + ROPE_HEADS, nh + 2 * nkvh);
@@ -138,11 +140,11 @@ static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, 
     if (nt == 0) return 0;
     dim3 grid(nt, (nh + 2 * nkvh + ROPE_HEADS - 1) / ROPE_HEADS);
     if (dh % 16 == 0 && (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc) & 15) == 0) {
-        rope_cache_vec_kernel<T><<<grid, 64, 0, s>>>((T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
+        TB_LAUNCH((rope_cache_vec_kernel<T>), grid, 64, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
                                                      (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
         return tb_last_error();
     }
-    rope_cache_kernel<T><<<grid, 128, 0, s>>>((T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
+    TB_LAUNCH((rope_cache_kernel<T>), grid, 128, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
                                             (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
     return tb_last_error();
 }

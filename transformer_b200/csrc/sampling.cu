@@ -130,6 +130,7 @@ __device__ Cut select_cut(const float* __restrict__ row, int V, float inv_t, flo
 __global__ void __launch_bounds__(SAMP_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ u, int V, float temperature,
               int top_k, float top_p, int* __restrict__ out_idx, float* __restrict__ out_val) {
+    pdl_sync();
     __shared__ float red_f[SAMP_THREADS];
     __shared__ int red_i[SAMP_THREADS];
     __shared__ int hist_c[256];
@@ -252,6 +253,6 @@ extern "C" int tb_sample(const float* logits, long long ld, const float* u, int 
     if (rows < 0 || V <= 0 || ld < V) return TB_ERR_ARG;
     if (!(temperature >= 0.f) || !(top_p > 0.f && top_p <= 1.f) || top_k < 0) return TB_ERR_ARG;
     if (rows == 0) return 0;
-    sample_kernel<<<rows, SAMP_THREADS, 0, s>>>(logits, ld, u, V, temperature, top_k, top_p, out_idx, out_val);
+    TB_LAUNCH((sample_kernel), rows, SAMP_THREADS, 0, s, logits, ld, u, V, temperature, top_k, top_p, out_idx, out_val);
     return tb_last_error();
 }
