@@ -228,7 +228,8 @@ def test_dispatch_grouped_products_and_combine(dtype, E, k, nt, d, di):
         assert float((out.double().cpu() - ref).abs().max()) <= 2 * _tol(dtype, float(ref.abs().max())), use
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 16, 8), (8, 50, 24), (9, 129, 104), (33, 688, 4096), (64, 4096, 688), (3, 1000, 72)])
+@pytest.mark.parametrize("M,N,K", [(1, 16, 8), (8, 50, 24), (9, 129, 104), (33, 688, 4096), (64, 4096, 688), (3, 1000, 72),
+                                   (17, 48, 1000)])
 def test_gemm_skinny_dense(M, N, K):
     from transformer_b200.parts.linear import gemm_skinny
     a, w = _rand((M, K), torch.bfloat16, 7), _rand((N, K), torch.bfloat16, 8, 0.1)

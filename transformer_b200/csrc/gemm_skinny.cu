@@ -56,11 +56,11 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
 // 16-byte loads in flight (the step is bound by memory latency x bytes in flight otherwise).
 template <int NT, bool DUAL, typename TY, int WK, int WN, int UNR>
 __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyArgs a) {
-    pdl_sync();
     constexpr int ROWS = 8 * NT;
     constexpr int NMAT = DUAL ? 2 : 1;
     __shared__ float red[WN][WK][NMAT][ROWS][SK_COLS + 1];
 
+    pdl_sync();
     const int g_idx = blockIdx.y;
     int row_lo = 0, row_hi = a.M;
     if (a.group_offsets) {
@@ -169,7 +169,11 @@ static int skinny_launch_shape(const SkinnyArgs& a, cudaStream_t s) {
     if (a.K >= 2048) {
         constexpr int WK = 8, WN = 1, UNR = NT >= 4 ? 2 : 4;
         dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
-        TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR>), grid, WK * WN * 32, 0, s, a);
+        // a grid too small to fill the GPU twice over: every thread keeps twice as many loads in flight
+        if (NT == 1 && !DUAL && (int)(grid.x * grid.y) <= 384)
+            TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, 8>), grid, WK * WN * 32, 0, s, a);
+        else
+            TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR>), grid, WK * WN * 32, 0, s, a);
     } else {
         constexpr int WK = 2, WN = 4, UNR = NT >= 4 ? 2 : 4;
         dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
