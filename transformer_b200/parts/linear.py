@@ -29,8 +29,8 @@ def gemm_simt(a, w, out, *, a_rows=None, group_offsets=None, groups=1, rows=None
 
 
 DENSE_TC = False           # dense bfloat16 products of many rows: this package's tcgen05 kernel instead of cuBLAS
-SKINNY_MAX_ROWS = 64       # dense: up to this many rows the weight-streaming kernel is used
-SKINNY_MAX_PAIRS = 512     # grouped: up to this many rows over all groups
+SKINNY_MAX_ROWS = 16       # dense: up to this many rows the weight-streaming kernel is used
+SKINNY_MAX_PAIRS = 128     # grouped: up to this many rows over all groups
 
 
 def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kind=0, max_group_rows=0) -> bool:
