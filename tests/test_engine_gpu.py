@@ -253,3 +253,20 @@ def test_command_line(folders):
     out = subprocess.run([sys.executable, "-m", "transformer_b200", "inspect", "--model", folders["B"]],
                          env=env, capture_output=True, text=True, cwd=ROOT)
     assert out.returncode == 0 and "nexp=6" in out.stdout and "architecture: llama" in out.stdout
+
+
+def test_a_gguf_file_gives_the_same_model(folders, tmp_path):
+    """The reference's own container: the same tensors under the same names load to the same logits."""
+    pytest.importorskip("gguf")
+    from safetensors.torch import load_file
+    from test_gguf import write_gguf
+    cfg, _ = CONFIGS["A"]
+    tensors = load_file(os.path.join(folders["A"], "model.safetensors"))
+    path = write_gguf(str(tmp_path / "a.gguf"), cfg, tensors)
+    prompt = random_prompts(cfg["vocab_size"], [20], seed=2)[0]
+    outs = []
+    for src in (folders["A"], path):
+        eng = tb.load(src, dtype="float32", max_tokens=128)
+        s = eng.open()
+        outs.append(eng.step([s], [prompt], [list(range(20))]).cpu())
+    assert float((outs[0] - outs[1]).abs().max()) < 2e-5      # epsilon travels as float32 in GGUF metadata

@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     int g = 0, row0 = 0, row_end = a.M;
     bool have_tile = true;
     if (a.group_offsets) {
-        int tile = blockIdx.x, cum = 0;
+        int tile = blockIdx.y, cum = 0;
         have_tile = false;
         for (g = 0; g < a.G; ++g) {
             const int lo = a.group_offsets[g], hi = a.group_offsets[g + 1];
@@ -164,12 +164,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             cum += tiles;
         }
     } else {
-        row0 = blockIdx.x * TC_BM;
+        row0 = blockIdx.y * TC_BM;
         have_tile = row0 < a.M;
     }
     if (!have_tile) return;   // the whole block leaves before any barrier or TMEM exists
     const int n_out = a.dual ? TC_BN / 2 : TC_BN;       // output columns of the tile
-    const int n0 = blockIdx.y * n_out;
+    const int n0 = blockIdx.x * n_out;   // column tiles of one row tile are neighbours in the grid: they share its A tile in L2
     const int nkb = (a.K + TC_BK - 1) / TC_BK;
 
     const uint32_t bar0 = smem_u32(bars);
@@ -380,7 +380,7 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1};
     const int n_out = dual ? TC_BN / 2 : TC_BN;
     const int tiles_m = group_offsets ? (M + TC_BM - 1) / TC_BM + G : (M + TC_BM - 1) / TC_BM;
-    dim3 grid(tiles_m, (N + n_out - 1) / n_out);
+    dim3 grid((N + n_out - 1) / n_out, tiles_m);
     TB_LAUNCH((gemm_tc_kernel), grid, TC_THREADS, smem, s, ma, mb, a);
     return tb_last_error();
 }

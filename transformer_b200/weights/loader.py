@@ -116,7 +116,8 @@ def check_rules(rules: Sequence[TensorRule], present: Mapping[str, Tuple[Tuple[i
             if tuple(shape) != tuple(want):
                 wrong_shape.append((n, tuple(shape), tuple(want)))
             is_int = dt.upper().startswith(("I", "U")) or dt.upper() == "BOOL"
-            if (rule.role == "table") != is_int or dt.upper() in ("F8_E4M3", "F8_E5M2", "BOOL"):
+            plain = dt.upper() in ("F32", "F16", "BF16", "F64")
+            if (rule.role == "table") != is_int or (not is_int and not plain):
                 wrong_type.append((n, dt, rule.role))
     unexpected = sorted(n for n in present if n not in used)
     if missing or unexpected or wrong_shape or wrong_type:
@@ -124,11 +125,19 @@ def check_rules(rules: Sequence[TensorRule], present: Mapping[str, Tuple[Tuple[i
     return chosen
 
 
+def open_tensors(path: str):
+    """The tensors of a model: a folder or file of safetensors, or one GGUF file."""
+    if os.path.isfile(path) and path.endswith(".gguf"):
+        from .gguf import GGufFile
+        return GGufFile(path)
+    return _Files(path)
+
+
 def load_weights(path: str, rules: Sequence[TensorRule], compute_dtype: torch.dtype,
                  device: torch.device) -> Dict[Dest, torch.Tensor]:
     """Read, check, convert and upload.  Returns {dest: device tensor}; a rule without a source in
     the file shares the tensor of ``shared_with``."""
-    files = _Files(path)
+    files = open_tensors(path)
     present = {n: files.shape_dtype(n) for n in files.names()}
     chosen = check_rules(rules, present, path)
     out: Dict[Dest, torch.Tensor] = {}
