@@ -92,7 +92,8 @@ class Attention(Mixer):
         group = self.nh // self.nkvh
         gc = 1 if group == 1 else 2 if group == 2 else 4
         blocks = nt * self.nkvh * ((group + gc - 1) // gc)
-        splits = int(max(1, min(32, (8 * ctx.engine.sm_count) // blocks)))
+        # enough blocks to fill the GPU eight times over, but no slice shorter than 128 keys of the longest sequence
+        splits = int(max(1, min(32, (8 * ctx.engine.sm_count) // blocks, ctx.max_len_after // 128)))
         partial = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
