@@ -46,6 +46,7 @@ struct TcArgs {
     int b_group_rows;   // rows of B per group in the stacked view (N, or 2N when dual)
     int dual;
     int out_float;
+    int tiles_m;        // row tiles (with groups: an upper bound; tiles past the last group are skipped)
 };
 
 // ---- small PTX wrappers ----------------------------------------------------------------------
@@ -136,87 +137,104 @@ __device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
 }
 
 // ---- the kernel ----------------------------------------------------------------------------
+// Persistent: a block walks the tiles  blockIdx.x, blockIdx.x + gridDim.x, ...  (column tiles of one row
+// tile are neighbours in that order, so concurrent blocks share its A tile in L2).  The TMA ring runs
+// on across tile boundaries, and there are TWO accumulators in TMEM: while the epilogue warps drain
+// tile i, the MMA warp already fills the other one with tile i + 1.
+struct TcTile {
+    int g, row0, row_end, n0;
+    bool valid;
+};
+
+__device__ __forceinline__ TcTile tc_tile(const TcArgs& a, int t, int tiles_n, int n_out) {
+    TcTile r;
+    const int tm = t / tiles_n;
+    r.n0 = (t - tm * tiles_n) * n_out;
+    r.g = 0;
+    r.row0 = tm * TC_BM;
+    r.row_end = a.M;
+    r.valid = r.row0 < a.M;
+    if (a.group_offsets) {
+        int cum = 0;
+        r.valid = false;
+        for (int g = 0; g < a.G; ++g) {
+            const int lo = a.group_offsets[g], hi = a.group_offsets[g + 1];
+            const int tiles = (hi - lo + TC_BM - 1) / TC_BM;
+            if (tm < cum + tiles) {
+                r.g = g;
+                r.row0 = lo + (tm - cum) * TC_BM;
+                r.row_end = hi;
+                r.valid = true;
+                break;
+            }
+            cum += tiles;
+        }
+    }
+    return r;
+}
+
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                             const __grid_constant__ CUtensorMap map_b,
                                                             const TcArgs a) {
     pdl_sync();
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * TC_STAGES + 1];
+    __shared__ __align__(8) uint64_t bars[2 * TC_STAGES + 4];
     __shared__ uint32_t tmem_slot;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    // which rows does this block own?
-    int g = 0, row0 = 0, row_end = a.M;
-    bool have_tile = true;
-    if (a.group_offsets) {
-        int tile = blockIdx.y, cum = 0;
-        have_tile = false;
-        for (g = 0; g < a.G; ++g) {
-            const int lo = a.group_offsets[g], hi = a.group_offsets[g + 1];
-            const int tiles = (hi - lo + TC_BM - 1) / TC_BM;
-            if (tile < cum + tiles) {
-                row0 = lo + (tile - cum) * TC_BM;
-                row_end = hi;
-                have_tile = true;
-                break;
-            }
-            cum += tiles;
-        }
-    } else {
-        row0 = blockIdx.y * TC_BM;
-        have_tile = row0 < a.M;
-    }
-    if (!have_tile) return;   // the whole block leaves before any barrier or TMEM exists
-    const int n_out = a.dual ? TC_BN / 2 : TC_BN;       // output columns of the tile
-    const int n0 = blockIdx.x * n_out;   // column tiles of one row tile are neighbours in the grid: they share its A tile in L2
+    const int n_out = a.dual ? TC_BN / 2 : TC_BN;       // output columns of a tile
+    const int tiles_n = (a.N + n_out - 1) / n_out;
+    const int total = a.tiles_m * tiles_n;
     const int nkb = (a.K + TC_BK - 1) / TC_BK;
 
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (TC_STAGES + s); };
-    const uint32_t acc_bar = bar0 + 8u * (2 * TC_STAGES);
+    auto acc_full = [&](int i) { return bar0 + 8u * (2 * TC_STAGES + i); };
+    auto acc_empty = [&](int i) { return bar0 + 8u * (2 * TC_STAGES + 2 + i); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(acc_bar, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(acc_full(i), 1);
+            mbar_init(acc_empty(i), 4);       // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TC_BN);
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), 2 * TC_BN);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_acc = tmem_slot;
+    const uint32_t tmem_base = tmem_slot;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            const int b_row = g * a.b_group_rows + n0;
             bool ok = true;
-            int issued = 0;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % TC_STAGES;
-                if (kb >= TC_STAGES) ok = mbar_wait(empty_bar(s), ((kb / TC_STAGES) - 1) & 1, a.error, 1);
-                if (!ok) break;
-                const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-                mbar_expect_tx(full_bar(s), TC_STAGE_BYTES);
-                tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, row0);
-                if (a.dual) {
+            int it = 0;                       // k-blocks handed to the ring so far, over all tiles
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const TcTile tl = tc_tile(a, t, tiles_n, n_out);
+                if (!tl.valid) continue;
+                const int b_row = tl.g * a.b_group_rows + tl.n0;
+                for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+                    const int s = it % TC_STAGES;
+                    if (it >= TC_STAGES) ok = mbar_wait(empty_bar(s), ((it / TC_STAGES) - 1) & 1, a.error, 1);
+                    if (!ok) break;
+                    const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    mbar_expect_tx(full_bar(s), TC_STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, tl.row0);
                     tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, b_row);
-                    tma_load_2d(sb + TC_B_BYTES / 2, &map_b, full_bar(s), kb * TC_BK, b_row + a.N);
-                } else {
-                    tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, b_row);
-                    tma_load_2d(sb + TC_B_BYTES / 2, &map_b, full_bar(s), kb * TC_BK, b_row + TC_BN / 2);
+                    tma_load_2d(sb + TC_B_BYTES / 2, &map_b, full_bar(s), kb * TC_BK,
+                                b_row + (a.dual ? a.N : TC_BN / 2));
                 }
-                issued = kb + 1;
             }
             if (*(volatile int*)a.error != 0) {
                 // something gave up: let this block's own copies land before the block goes away
-                for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb)
-                    mbar_wait(full_bar(kb % TC_STAGES), (kb / TC_STAGES) & 1, a.error, 4);
+                for (int i = max(0, it - TC_STAGES); i < it; ++i)
+                    mbar_wait(full_bar(i % TC_STAGES), (i / TC_STAGES) & 1, a.error, 4);
             }
         }
     } else if (warp == 1) {
@@ -224,29 +242,46 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(TC_BM, TC_BN);
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % TC_STAGES;
-                ok = mbar_wait(full_bar(s), (kb / TC_STAGES) & 1, a.error, 2);
+            int it = 0, lt = 0;               // k-blocks and tiles done by this block
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const TcTile tl = tc_tile(a, t, tiles_n, n_out);
+                if (!tl.valid) continue;
+                const int buf = lt & 1;
+                if (lt >= 2) ok = mbar_wait(acc_empty(buf), ((lt >> 1) - 1) & 1, a.error, 5);   // drained two tiles ago
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-                const uint64_t da = umma_desc(sa), db = umma_desc(sb);
+                const uint32_t acc = tmem_base + buf * TC_BN;
+                for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+                    const int s = it % TC_STAGES;
+                    ok = mbar_wait(full_bar(s), (it / TC_STAGES) & 1, a.error, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    const uint64_t da = umma_desc(sa), db = umma_desc(sb);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along K: +2 in units of 16 bytes
-                    umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-                umma_commit(empty_bar(s));             // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along K: +2 in units of 16 bytes
+                        umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit(empty_bar(s));             // the stage is free once these MMAs have read it
+                }
+                umma_commit(acc_full(buf));                // the accumulator is complete (or abandoned)
+                ++lt;
             }
-            umma_commit(acc_bar);                      // the accumulator is complete (or abandoned)
         }
     } else {
         // ---------------- epilogue: warps 2..5, TMEM lanes 32 * (warp % 4) ----------------
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
-        const int m = row0 + row;
-        const bool ok = mbar_wait(acc_bar, 0, a.error, 3);
-        tc_fence_after();
-        if (ok) {
-            const uint32_t trow = tmem_acc + ((uint32_t)(quad * 32) << 16);
+        bool ok = true;
+        int lt = 0;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            const TcTile tl = tc_tile(a, t, tiles_n, n_out);
+            if (!tl.valid) continue;
+            const int buf = lt & 1;
+            const int m = tl.row0 + row, n0 = tl.n0;
+            ok = mbar_wait(acc_full(buf), (lt >> 1) & 1, a.error, 3);
+            tc_fence_after();
+            if (!ok) break;
+            const uint32_t trow = tmem_base + buf * TC_BN + ((uint32_t)(quad * 32) << 16);
             for (int c0 = 0; c0 < n_out; c0 += 32) {
                 float v[32];
                 tmem_ld32(trow + c0, v);               // warp-collective: every lane takes part
@@ -256,7 +291,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
                 }
-                if (m < row_end && n0 + c0 < a.N) {
+                if (m < tl.row_end && n0 + c0 < a.N) {
                     if (a.out_float) {
                         float* dst = static_cast<float*>(a.C) + (size_t)m * a.ldc + n0 + c0;
 #pragma unroll
@@ -286,11 +321,16 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                 }
             }
+            // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+            ++lt;
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_acc, TC_BN);
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * TC_BN);
 }
 
 // Gather rows: out[m, :] = x[rows[m], :]  (activations sorted by expert, so that TMA can fetch tiles)
@@ -377,16 +417,24 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1};
     const int n_out = dual ? TC_BN / 2 : TC_BN;
     const int tiles_m = group_offsets ? (M + TC_BM - 1) / TC_BM + G : (M + TC_BM - 1) / TC_BM;
-    dim3 grid((N + n_out - 1) / n_out, tiles_m);
-    TB_LAUNCH((gemm_tc_kernel), grid, TC_THREADS, smem, s, ma, mb, a);
+    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, tiles_m};
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 1;
+    }
+    const int total = tiles_m * ((N + n_out - 1) / n_out);
+    const int blocks = total < sms ? total : sms;     // one persistent block per SM
+    TB_LAUNCH((gemm_tc_kernel), blocks, TC_THREADS, smem, s, ma, mb, a);
     return tb_last_error();
 }
 
 // Nonzero if any tensor-core product gave up on a wait since the last call (1 producer, 2 MMA,
-// 3 epilogue, 4 drain); reading it synchronises the device and clears it.
+// 3 epilogue, 4 drain, 5 accumulator hand-back); reading it synchronises the device and clears it.
 int tb_gemm_tc_status() {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, tc_error_word, sizeof(int)) != cudaSuccess) return -1;
