@@ -7,7 +7,7 @@
 //
 // A block = one tile of up to 64 query tokens of ONE sequence x one query head; its 4 warps own 16
 // query rows each.  It walks the sequence's pages (64 keys each): K and V of a page are copied to
-// shared memory with cp.async (double buffered, 128-byte XOR swizzle), S = Q K^T and O += P V run
+// shared memory with cp.async (K double buffered, V fetched behind the score product; XOR swizzle), S = Q K^T and O += P V run
 // as mma.sync.m16n8k16 with ldmatrix-fed fragments, and the softmax is the online form kept in
 // registers.  The step's own keys are already in the cache.
 // Head sizes 64 and 128; others are answered with TB_ERR_UNSUPPORTED and the caller takes the
@@ -62,14 +62,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int DH>
-__global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(const PrefillArgs a) {
+__global__ void __launch_bounds__(AP_THREADS, 3) attention_prefill_kernel(const PrefillArgs a) {
     pdl_sync();
     constexpr int CH = DH / 8;                 // 16-byte chunks in a row
     constexpr int TILE = AP_BN * DH;           // elements of one K or V tile
     extern __shared__ __align__(128) __nv_bfloat16 sm[];
     __nv_bfloat16* sq = sm;                    // [64][DH]
-    __nv_bfloat16* sk = sq + AP_BM * DH;       // [2][64][DH]
-    __nv_bfloat16* sv = sk + 2 * TILE;         // [2][64][DH]
+    __nv_bfloat16* sk = sq + AP_BM * DH;       // [2][64][DH]  K of tile j and of tile j + 1
+    __nv_bfloat16* sv = sk + 2 * TILE;         // [64][DH]     V of tile j only: three blocks fit on an SM
     // element offset of (row, 16-byte chunk) under the XOR swizzle
     auto swz = [](int row, int chunk) { return row * DH + ((chunk ^ (row & 7)) << 3); };
 
@@ -84,17 +84,12 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(const Pre
     const int gid = lane >> 2, tid4 = lane & 3;
     const int* pt = a.page_table + (size_t)b * a.max_pages;
 
-    auto load_kv = [&](int j, int buf) {
-        const size_t base = ((size_t)pt[j] * a.nkvh + g) * TB_PAGE * DH;
-        const __nv_bfloat16* ksrc = a.kc + base;
-        const __nv_bfloat16* vsrc = a.vc + base;
-        const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(sk + buf * TILE);
-        const uint32_t vdst = (uint32_t)__cvta_generic_to_shared(sv + buf * TILE);
+    auto load_tile = [&](const __nv_bfloat16* cache, int j, __nv_bfloat16* dst_tile) {
+        const __nv_bfloat16* src = cache + ((size_t)pt[j] * a.nkvh + g) * TB_PAGE * DH;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(dst_tile);
         for (int idx = threadIdx.x; idx < AP_BN * CH; idx += AP_THREADS) {
             const int row = idx / CH, c = idx - row * CH;
-            const int off = swz(row, c);
-            cp_async16(kdst + off * 2, ksrc + row * DH + c * 8);
-            cp_async16(vdst + off * 2, vsrc + row * DH + c * 8);
+            cp_async16(dst + swz(row, c) * 2, src + row * DH + c * 8);
         }
     };
 
@@ -105,7 +100,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(const Pre
         if (row < nq) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(t0 + row) * a.q_stride + (size_t)h * DH + c * 8);
         *reinterpret_cast<uint4*>(sq + swz(row, c)) = v;
     }
-    load_kv(0, 0);
+    load_tile(a.kc, 0, sk);
     cp_async_commit();
 
     float o[DH / 8][4];
@@ -121,11 +116,13 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(const Pre
     for (int j = 0; j < n_tiles; ++j) {
         const int buf = j & 1;
         cp_async_wait<0>();
-        __syncthreads();                       // tile j has landed; everyone is done with tile j - 1
-        if (j + 1 < n_tiles) load_kv(j + 1, buf ^ 1);
+        __syncthreads();                       // K of tile j has landed; everyone is done with tile j - 1 (its V too)
+        load_tile(a.vc, j, sv);                // V of tile j flies while S = Q K^T is computed
+        cp_async_commit();
+        if (j + 1 < n_tiles) load_tile(a.kc, j + 1, sk + (buf ^ 1) * TILE);
         cp_async_commit();
         const uint32_t sk_addr = (uint32_t)__cvta_generic_to_shared(sk + buf * TILE);
-        const uint32_t sv_addr = (uint32_t)__cvta_generic_to_shared(sv + buf * TILE);
+        const uint32_t sv_addr = (uint32_t)__cvta_generic_to_shared(sv);
 
         // ---- S = Q K^T : 16 rows x 64 keys per warp ----
         float s[AP_BN / 8][4];
@@ -199,6 +196,8 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(const Pre
             p[nb][1] = pack_bf16(p2, p3);
         }
         // ---- O += P V ----
+        cp_async_wait<1>();                    // all but the newest group (K of tile j + 1): V of tile j is here
+        __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < AP_BN / 16; ++kk) {
             const uint32_t a0 = p[2 * kk][0], a1 = p[2 * kk][1], a2 = p[2 * kk + 1][0], a3 = p[2 * kk + 1][1];
@@ -238,7 +237,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(const Pre
 
 template <int DH>
 static int prefill_launch(const PrefillArgs& a, cudaStream_t s) {
-    const size_t smem = (size_t)(AP_BM * DH + 4 * AP_BN * DH) * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(AP_BM * DH + 3 * AP_BN * DH) * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
