@@ -270,3 +270,16 @@ def test_a_gguf_file_gives_the_same_model(folders, tmp_path):
         s = eng.open()
         outs.append(eng.step([s], [prompt], [list(range(20))]).cpu())
     assert float((outs[0] - outs[1]).abs().max()) < 2e-5      # epsilon travels as float32 in GGUF metadata
+
+
+def test_a_step_that_wants_nothing_still_fills_the_cache(folders):
+    cfg, _ = CONFIGS["A"]
+    _, tensors = P.read_folder(folders["A"])
+    eng = tb.load(folders["A"], dtype="float32", max_tokens=128)
+    p = random_prompts(cfg["vocab_size"], [12], seed=4)[0]
+    s = eng.open()
+    out = eng.step([s], [p[:8]], [[]])
+    assert tuple(out.shape) == (0, cfg["vocab_size"]) and eng.cache.length(s) == 8
+    lg = eng.step([s], [p[8:]], [[0, 3]]).cpu()
+    ref = P.forward(cfg, tensors, p, want=[8, 11])
+    assert float((lg - ref).abs().max()) <= FP32_TOL

@@ -14,9 +14,14 @@
 //    (swiglu, compute.rs:324-326).
 //  * output bfloat16 or float (logits, router).
 //
-// One block = 16 output columns of one group.  Its 8 warps split K (warp w takes the 32-wide
-// k-steps w, w + 8, ...: neighbouring warps read neighbouring 64-byte pieces of a weight row) and
-// add their partial sums through shared memory.  Rows are taken 8 * NT at a time.
+// A block covers 16 * WN output columns of one group.  WK warps split K (warp w takes the 32-wide
+// k-steps w, w + WK, ...: neighbouring warps read neighbouring 64-byte pieces of a weight row) and
+// add their partial sums through shared memory; long rows use 8 x 1 warps, short ones (an expert's
+// down projection) 2 x 4.  Rows are taken 8 * NT at a time.  What bounds the kernel is the number of
+// bytes in flight, so every thread issues UNR k-steps of loads before it multiplies any of them.
+// (Measured and dropped: staging the weights through shared memory with cp.async, persistent or
+// not; cp.async.bulk.prefetch.L2 of the block's weight rows; a tcgen05 variant with the weights as
+// the M = 128 side behind a 12-stage TMA ring.  All were correct and all were slower than this.)
 //
 // The 8 values a thread loads per row with one 16-byte load are consecutive in k; the mma's
 // k-slots are fed in that order for both operands (a dot product does not care about the order of

@@ -16,9 +16,6 @@ from safetensors import safe_open
 
 from .plan import Dest, Source, TensorRule
 
-_FLOATS = (torch.float32, torch.float16, torch.bfloat16, torch.float64)
-_INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
-
 
 class WeightError(RuntimeError):
     """One error for everything that is wrong with a weight file."""
