@@ -52,6 +52,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsig
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Weights are read once: no L1 allocation, and each L2 miss brings 256 bytes from HBM (its neighbours
+// are wanted a moment later by the next warps).
+__device__ __forceinline__ uint4 ld16w(const __nv_bfloat16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
     return *reinterpret_cast<const uint4*>(p);
 }
@@ -113,11 +121,11 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
             for (int u = 0; u < UNR; ++u) {
                 const int k = (s0 + u * WK) * 32;
                 const bool live = k + t * 8 < a.K;      // also false past the last step
-                wa[u] = live ? ld16(w0 + k) : zero4;
-                wb[u] = live ? ld16(w1 + k) : zero4;
+                wa[u] = live ? ld16w(w0 + k) : zero4;
+                wb[u] = live ? ld16w(w1 + k) : zero4;
                 if (DUAL) {
-                    ua[u] = live ? ld16(u0 + k) : zero4;
-                    ub[u] = live ? ld16(u1 + k) : zero4;
+                    ua[u] = live ? ld16w(u0 + k) : zero4;
+                    ub[u] = live ? ld16w(u1 + k) : zero4;
                 }
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) xv[u][nt] = (live && nt < nta && xp[nt]) ? ld16(xp[nt] + k) : zero4;
