@@ -397,3 +397,24 @@ def test_attention_prompt_kernel(nh, nkvh, dh):
                             c["vc"].data_ptr(), c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(),
                             c["tile_nq"].data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(), c["tiles"],
                             c["max_pages"], nh * 48, nh, c["nkvh"], 48, 1.0)
+
+
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 64), (8, 8, 128), (6, 1, 128)])
+def test_attention_tcgen05_kernel(nh, nkvh, dh):
+    """The tcgen05 prompt kernel (S and O in tensor memory) on a ragged batch: prompts from zero, shorter and
+    longer than its 128-token tile, a continued prompt over 130 cached tokens, a single token."""
+    import os
+    lib = _lib()
+    dtype = torch.bfloat16
+    tq = lib.attention_tc_tile_tokens()
+    c = attention_case([150, 1, 64, 37, 300], [0, 90, 0, 130, 64], nh, nkvh, dh, dtype, tq, seed=nh + dh)
+    nt = c["nt"]
+    out = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
+    assert lib.try_call("tb_attention_tc_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
+                        c["vc"].data_ptr(), c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(), c["tile_nq"].data_ptr(),
+                        c["tok_pos"].data_ptr(), c["table"].data_ptr(), c["tiles"], nt, c["max_pages"], nh * dh, nh,
+                        c["nkvh"], dh, c["kc"].shape[0], 1.0 / math.sqrt(dh), int(os.environ.get("TB_V_LBO", "0")),
+                        int(os.environ.get("TB_V_SBO", "0")))
+    assert lib.gemm_tc_status() == 0, "a wait inside the kernel gave up"
+    got = out.double().cpu().reshape(nt, nh, dh)
+    assert float((got - c["ref"]).abs().max()) <= _tol(dtype, 4.0)

@@ -1,0 +1,341 @@
+// Causal attention for prompts over the paged cache on the 5th-generation tensor cores (tcgen05),
+// bfloat16 in, float accumulation in tensor memory.
+//
+// Same mathematics as the other attention kernels (score = q.k / sqrt(dh) over positions <= the
+// token's own, models/llama/common/src/compute.rs:243-264; softmax statistics and the output
+// accumulator in float).  A block = 128 query tokens of ONE sequence x one query head; it walks the
+// sequence's pages (64 keys each):
+//
+//   warp 0   TMA: the Q tile once, then K and V of each page into a two-stage ring (the cache of a
+//            layer is one 2-D tensor [pages * nkvh * 64, dh], so a page of a head is a box of rows)
+//   warp 1   one thread issues  S = Q K^T  (128 x 64, accumulator S in TMEM) and  O += P V
+//            (128 x dh, accumulator O in TMEM; V is the MN-major B operand, straight as cached)
+//   warps 2-5  128 threads = the 128 query rows: read their row of S from TMEM, mask, running
+//            maximum and sum, P = exp2(s - m) rounded to bfloat16 into shared memory (swizzled as
+//            the A operand wants it), and at the end O / l to memory.
+//
+// The running maximum is only raised when it grows by more than 8 (in the exponent's log2 units):
+// then the row of O in TMEM is rescaled; otherwise P is simply computed against the older maximum
+// (it stays below 2^8, exact enough in bfloat16 and float), so the costly read-modify-write of O is
+// rare.  Every wait on an mbarrier is bounded (see gemm_tc.cu); a wait that runs out sets the error
+// word that tb_gemm_tc_status() reports.
+//
+// Head sizes 64 and 128.
+#include <cuda.h>
+
+#include "tc_common.cuh"
+
+#define AT_BM 128
+#define AT_BN 64
+#define AT_STAGES 2
+#define AT_THREADS 192
+
+struct AtArgs {
+    __nv_bfloat16* out;       // [nt, nh * dh]
+    const int* tile_seq;
+    const int* tile_t0;
+    const int* tile_nq;
+    const int* tok_pos;
+    const int* page_table;
+    int* error;
+    int tiles, max_pages, nh, nkvh;
+    float scale_log2e;
+    unsigned v_lbo, v_sbo;    // descriptor strides of the MN-major V operand, in bytes
+};
+
+// Shared-memory descriptor with explicit strides (K-major operands use umma_desc of tc_common.cuh).
+__device__ __forceinline__ uint64_t umma_desc_strides(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <int DH>
+__global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                 const __grid_constant__ CUtensorMap map_k,
+                                                                 const __grid_constant__ CUtensorMap map_v,
+                                                                 const AtArgs a) {
+    pdl_sync();
+    constexpr int KB = DH / 64;                          // 64-wide column boxes of a row of dh values
+    constexpr uint32_t Q_BYTES = AT_BM * DH * 2, KV_BYTES = AT_BN * DH * 2, P_BYTES = AT_BM * AT_BN * 2;
+    constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;
+    constexpr uint32_t TMEM_COLS = (AT_BN + DH) <= 128 ? 128 : 256;
+    // All shared memory is dynamic and the kernel has no static shared memory, so the tiles start at the
+    // base of the block's window (1024-byte aligned, as the 128-byte swizzle needs); two blocks then fit
+    // on an SM.  The barriers and the TMEM slot follow the tiles.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = smem_u32(smem_raw);
+    const uint32_t sq = smem_base, sp = sq + Q_BYTES, skv = sp + P_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + Q_BYTES + P_BYTES + AT_STAGES * STAGE_BYTES);
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 2 * AT_STAGES + 4);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (smem_base & 1023u) {                              // never expected; refuse rather than compute garbage
+        if (threadIdx.x == 0) atomicCAS(a.error, 0, 19);
+        return;
+    }
+
+    const int tile = a.tiles - 1 - (int)blockIdx.x;      // the tiles that see the most keys start first
+    const int h = blockIdx.y, g = h / (a.nh / a.nkvh);
+    const int b = a.tile_seq[tile], t0 = a.tile_t0[tile], nq = a.tile_nq[tile];
+    const int pos_first = a.tok_pos[t0], pos_last = pos_first + nq - 1;
+    const int n_tiles = pos_last / AT_BN + 1;
+    const int* pt = a.page_table + (size_t)b * a.max_pages;
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto kv_full = [&](int s) { return bar0 + 8u * s; };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (AT_STAGES + s); };
+    const uint32_t q_full = bar0 + 8u * (2 * AT_STAGES), s_full = q_full + 8, p_ready = q_full + 16, o_done = q_full + 24;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < AT_STAGES; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        mbar_init(q_full, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_ready, 4);       // one arrival per softmax warp
+        mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + AT_BN;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) tma_load_2d(sq + kb * (AT_BM * 128), &map_q, q_full, h * DH + kb * 64, t0);
+            bool ok = true;
+            int issued = 0;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % AT_STAGES;
+                if (j >= AT_STAGES) ok = mbar_wait(kv_empty(s), ((j / AT_STAGES) - 1) & 1, a.error, 11);
+                if (!ok) break;
+                const int row = (pt[j] * a.nkvh + g) * TB_PAGE;
+                const uint32_t sk = skv + s * STAGE_BYTES, sv = sk + KV_BYTES;
+                mbar_expect_tx(kv_full(s), STAGE_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+                    tma_load_2d(sk + kb * (AT_BN * 128), &map_k, kv_full(s), kb * 64, row);
+                    tma_load_2d(sv + kb * (AT_BN * 128), &map_v, kv_full(s), kb * 64, row);
+                }
+                issued = j + 1;
+            }
+            if (*(volatile int*)a.error != 0) {
+                mbar_wait(q_full, 0, a.error, 14);
+                for (int j = max(0, issued - AT_STAGES); j < issued; ++j)
+                    mbar_wait(kv_full(j % AT_STAGES), (j / AT_STAGES) & 1, a.error, 14);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(AT_BM, AT_BN);                       // both operands K-major
+            const uint32_t idesc_o = umma_idesc(AT_BM, DH) | (1u << 16);             // B (= V) is MN-major
+            bool ok = mbar_wait(q_full, 0, a.error, 12);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % AT_STAGES;
+                ok = mbar_wait(kv_full(s), (j / AT_STAGES) & 1, a.error, 12);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sk = skv + s * STAGE_BYTES, sv = sk + KV_BYTES;
+                // S = Q K^T: K = dh in steps of 16; step k lives in column box k / 4, 32 bytes * (k % 4) along the row
+#pragma unroll
+                for (int k = 0; k < DH / 16; ++k) {
+                    const uint64_t dq = umma_desc(sq + (k / 4) * (AT_BM * 128)) + 2 * (k % 4);
+                    const uint64_t dk = umma_desc(sk + (k / 4) * (AT_BN * 128)) + 2 * (k % 4);
+                    umma_bf16(tmem_s, dq, dk, idesc_s, k != 0);
+                }
+                umma_commit(s_full);
+                ok = mbar_wait(p_ready, j & 1, a.error, 13);       // P is in shared memory (and S has been read)
+                if (!ok) break;
+                tc_fence_after();
+                // O += P V: K = 64 keys in steps of 16 (16 keys = two 8-row groups = 2048 bytes along V's rows;
+                // 32 bytes along P's rows); N = dh spans KB column boxes of V
+#pragma unroll
+                for (int k = 0; k < AT_BN / 16; ++k) {
+                    const uint64_t dp = umma_desc(sp) + 2 * k;
+                    const uint64_t dv = umma_desc_strides(sv + k * 2048, a.v_lbo, a.v_sbo);
+                    umma_bf16(tmem_o, dp, dv, idesc_o, (j | k) != 0);
+                }
+                umma_commit(kv_empty(s));
+                umma_commit(o_done);
+            }
+        }
+    } else {
+        // ---------------- softmax / correction / epilogue: thread = query row ----------------
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int pos_r = pos_first + row;
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        float m_used = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            ok = mbar_wait(s_full, j & 1, a.error, 15);
+            tc_fence_after();
+            if (!ok) break;
+            float s[AT_BN];
+            {
+                float lo[32], hi[32];
+                tmem_ld32(tmem_s + lane_sel, lo);
+                tmem_ld32(tmem_s + lane_sel + 32, hi);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    s[i] = lo[i];
+                    s[32 + i] = hi[i];
+                }
+            }
+            const int key0 = j * AT_BN;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < AT_BN; ++i) {
+                s[i] = (key0 + i <= pos_r) ? s[i] * a.scale_log2e : -INFINITY;
+                mx = fmaxf(mx, s[i]);
+            }
+            // raise the maximum only when it has grown by more than 8; then O must be rescaled
+            const bool raise = mx > m_used + 8.0f;          // also true for the first visible keys (m_used = -inf)
+            const float m_new = raise ? mx : m_used;
+            // the previous tile's P V must be done before P is overwritten and before O is touched
+            if (j > 0) {
+                ok = mbar_wait(o_done, (j - 1) & 1, a.error, 16);
+                tc_fence_after();
+                if (!ok) break;
+            }
+            if (__any_sync(0xffffffffu, raise && j > 0 && m_used != -INFINITY)) {
+                const float f = (m_used == -INFINITY) ? 1.0f : exp2f(m_used - m_new);
+                l_run *= f;
+#pragma unroll
+                for (int c0 = 0; c0 < DH; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_sel + c0, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= f;
+                    tmem_st32(tmem_o + lane_sel + c0, o);
+                }
+            } else if (raise && m_used != -INFINITY) {
+                l_run *= exp2f(m_used - m_new);              // j == 0 cannot get here; kept for symmetry
+            }
+            m_used = m_new;
+            const float mref = (m_used == -INFINITY) ? 0.f : m_used;
+            // P = exp2(s - m) as bfloat16 into the A-operand tile [128 rows x 64 keys], 128-byte swizzle:
+            // row r at r * 128 bytes, its 16-byte chunk c at ((c ^ (r & 7)) * 16)
+            const uint32_t prow = sp + row * 128;
+#pragma unroll
+            for (int c = 0; c < AT_BN / 8; ++c) {
+                float p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    p[i] = exp2f(s[c * 8 + i] - mref);
+                    l_run += p[i];
+                }
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0], p[1]), h1 = __floats2bfloat162_rn(p[2], p[3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p[4], p[5]), h3 = __floats2bfloat162_rn(p[6], p[7]);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((c ^ (row & 7)) << 4)),
+                             "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                             "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+                             : "memory");
+            }
+            // make the generic-proxy writes of P visible to the tensor core (async proxy), then signal
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_ready) : "memory");
+        }
+        if (ok) {
+            ok = mbar_wait(o_done, (n_tiles - 1) & 1, a.error, 17);
+            tc_fence_after();
+        }
+        if (ok) {
+            const float inv = 1.0f / l_run;
+            __nv_bfloat16* dst = a.out + ((size_t)(t0 + row) * a.nh + h) * DH;
+#pragma unroll
+            for (int c0 = 0; c0 < DH; c0 += 32) {
+                float o[32];
+                tmem_ld32(tmem_o + lane_sel + c0, o);       // warp-collective: rows past nq take part, store nothing
+                if (row < nq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        float f8[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f8[e] = o[i + e] * inv;
+                        store8(dst + c0 + i, f8);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_slot, TMEM_COLS);
+}
+
+template <int DH>
+static int attention_tc_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AtArgs& a,
+                               cudaStream_t s) {
+    const size_t smem = (size_t)AT_BM * DH * 2 + AT_BM * AT_BN * 2 + (size_t)AT_STAGES * 2 * AT_BN * DH * 2 + 128;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(a.tiles, a.nh);
+    TB_LAUNCH((attention_tc_kernel<DH>), grid, AT_THREADS, smem, s, mq, mk, mv, a);
+    return tb_last_error();
+}
+
+extern "C" {
+// Query tiles hold up to this many tokens of one sequence.
+int tb_attention_tc_tile_tokens() { return AT_BM; }
+
+// q: [nt, q_stride] (first q head of each token), out: [nt, nh * dh], kc / vc: one layer's cache
+// [cache_pages, nkvh, 64, dh].  v_lbo / v_sbo: 0 = the built-in strides of the V operand's descriptor.
+int tb_attention_tc_bf16(const void* q, void* out, const void* kc, const void* vc, const int* tile_seq,
+                         const int* tile_t0, const int* tile_nq, const int* tok_pos, const int* page_table, int tiles,
+                         int nt, int max_pages, int q_stride, int nh, int nkvh, int dh, int cache_pages, float scale,
+                         int v_lbo, int v_sbo, cudaStream_t s) {
+    if (nh <= 0 || nkvh <= 0 || nh % nkvh || tiles < 0 || nt < 0 || cache_pages <= 0) return TB_ERR_ARG;
+    if (dh != 64 && dh != 128) return TB_ERR_UNSUPPORTED;
+    if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kc | (uintptr_t)vc) & 15)) return TB_ERR_UNSUPPORTED;
+    if (tiles == 0) return 0;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map(&mq, q, nt, nh * dh, q_stride, AT_BM);
+    if (rc) return rc;
+    const long long rows = (long long)cache_pages * nkvh * TB_PAGE;
+    rc = make_map(&mk, kc, rows, dh, dh, AT_BN);
+    if (rc) return rc;
+    rc = make_map(&mv, vc, rows, dh, dh, AT_BN);
+    if (rc) return rc;
+    int* err_ptr = tc_error_ptr();
+    if (!err_ptr) return TB_ERR_UNSUPPORTED;
+    AtArgs a{(__nv_bfloat16*)out, tile_seq, tile_t0, tile_nq, tok_pos, page_table, err_ptr, tiles, max_pages, nh, nkvh,
+             scale * 1.4426950408889634f, (unsigned)(v_lbo ? v_lbo : AT_BN * 128), (unsigned)(v_sbo ? v_sbo : 1024)};
+    return dh == 64 ? attention_tc_launch<64>(mq, mk, mv, a, s) : attention_tc_launch<128>(mq, mk, mv, a, s);
+}
+}

@@ -31,13 +31,15 @@ _SIGNATURES: Dict[str, str] = {
     "tb_gemm_skinny_bf16": "pppppliiiiiiiii",
     "tb_attention_decode_f32": "ppppppppiiiiiiif", "tb_attention_decode_bf16": "ppppppppiiiiiiif",
     "tb_attention_prefill_bf16": "pppppppppiiiiiif",
+    "tb_attention_tc_bf16": "pppppppppiiiiiiiifii",
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
     "tb_router_f32": "pppppiiii", "tb_router_bf16": "pppppiiii",
     "tb_moe_dispatch": "ppppiii", "tb_topk_softmax": "pppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
     "tb_sample": "plpiififpp",
 }
-_NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": ""}
+_NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
+              "tb_attention_tc_tile_tokens": ""}
 
 _lock = threading.Lock()
 _lib = None
@@ -133,3 +135,7 @@ def gemm_tc_status() -> int:
 
 def attention_prefill_tile_tokens() -> int:
     return library().tb_attention_prefill_tile_tokens()
+
+
+def attention_tc_tile_tokens() -> int:
+    return library().tb_attention_tc_tile_tokens()

@@ -16,6 +16,9 @@ from .linear import matmul_nt
 from .spec import PartSpec
 
 
+USE_TCGEN05 = True     # prompts: the tcgen05 kernel before the mma.sync one
+
+
 @MIXERS.register("attention")
 class Attention(Mixer):
     """params: width, nh, nkvh, dh, position (a PartSpec of a rotary encoding, or None)."""
@@ -37,7 +40,8 @@ class Attention(Mixer):
         # query tiles this mixer asks the step to plan: the general kernel's, and the prompt kernel's
         self.general_tile = lib.attention_tile_tokens(self.nh, self.nkvh)
         self.prompt_tile = lib.attention_prefill_tile_tokens() if (dtype == torch.bfloat16 and self.dh in (64, 128)) else 0
-        self.tile_sizes = [self.general_tile] + ([self.prompt_tile] if self.prompt_tile else [])
+        self.tc_tile = lib.attention_tc_tile_tokens() if self.prompt_tile else 0
+        self.tile_sizes = [self.general_tile] + ([self.prompt_tile, self.tc_tile] if self.prompt_tile else [])
 
     def parameters(self):
         return {
@@ -68,6 +72,15 @@ class Attention(Mixer):
         if ctx.decode and self._decode_kernel(ctx, qkv, o, cache, table, nt, sfx):
             matmul_nt(o, self.weights["wo"], out)
             return
+        if self.tc_tile and nt >= 2 * ctx.B and USE_TCGEN05:
+            # prompts: S and O in tensor memory, K and V pages by TMA
+            tiles = ctx.tiles(self.tc_tile)
+            if lib.try_call("tb_attention_tc_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                            lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos),
+                            lib.ptr(table), tiles.count, nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh,
+                            self.dh, cache.k.shape[0], self.scale, 0, 0):
+                matmul_nt(o, self.weights["wo"], out)
+                return
         if self.prompt_tile and nt >= 2 * ctx.B:
             tiles = ctx.tiles(self.prompt_tile)
             if lib.try_call("tb_attention_prefill_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
