@@ -82,15 +82,15 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
     constexpr int KB = DH / 64;                          // 64-wide column boxes of a row of dh values
     constexpr uint32_t Q_BYTES = AT_BM * DH * 2, KV_BYTES = AT_BN * DH * 2, P_BYTES = AT_BM * AT_BN * 2;
     constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;
-    constexpr uint32_t TMEM_COLS = (AT_BN + DH) <= 128 ? 128 : 256;
+    constexpr uint32_t TMEM_COLS = 256;                  // S twice (2 x 64 columns) and O (dh columns)
     // All shared memory is dynamic and the kernel has no static shared memory, so the tiles start at the
     // base of the block's window (1024-byte aligned, as the 128-byte swizzle needs); two blocks then fit
     // on an SM.  The barriers and the TMEM slot follow the tiles.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
     const uint32_t sq = smem_base, sp = sq + Q_BYTES, skv = sp + P_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + Q_BYTES + P_BYTES + AT_STAGES * STAGE_BYTES);
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 2 * AT_STAGES + 4);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + Q_BYTES + P_BYTES + AT_STAGES * STAGE_BYTES);   // 2 * stages + 5
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 2 * AT_STAGES + 5);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (smem_base & 1023u) {                              // never expected; refuse rather than compute garbage
         if (threadIdx.x == 0) atomicCAS(a.error, 0, 19);
@@ -107,14 +107,16 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
     const uint32_t bar0 = smem_u32(bars);
     auto kv_full = [&](int s) { return bar0 + 8u * s; };
     auto kv_empty = [&](int s) { return bar0 + 8u * (AT_STAGES + s); };
-    const uint32_t q_full = bar0 + 8u * (2 * AT_STAGES), s_full = q_full + 8, p_ready = q_full + 16, o_done = q_full + 24;
+    const uint32_t q_full = bar0 + 8u * (2 * AT_STAGES), p_ready = q_full + 8, o_done = q_full + 16;
+    auto s_full = [&](int i) { return q_full + 24 + 8u * i; };      // one per S buffer
     if (threadIdx.x == 0) {
         for (int s = 0; s < AT_STAGES; ++s) {
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
         }
         mbar_init(q_full, 1);
-        mbar_init(s_full, 1);
+        mbar_init(s_full(0), 1);
+        mbar_init(s_full(1), 1);
         mbar_init(p_ready, 4);       // one arrival per softmax warp
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + AT_BN;
+    const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + 2 * AT_BN;     // S of tile j at tmem_s + (j & 1) * 64
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -158,24 +160,37 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(AT_BM, AT_BN);                       // both operands K-major
             const uint32_t idesc_o = umma_idesc(AT_BM, DH) | (1u << 16);             // B (= V) is MN-major
-            bool ok = mbar_wait(q_full, 0, a.error, 12);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % AT_STAGES;
-                ok = mbar_wait(kv_full(s), (j / AT_STAGES) & 1, a.error, 12);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t sk = skv + s * STAGE_BYTES, sv = sk + KV_BYTES;
-                // S = Q K^T: K = dh in steps of 16; step k lives in column box k / 4, 32 bytes * (k % 4) along the row
+            // S = Q K^T of tile j into S buffer j & 1: K = dh in steps of 16; step k lives in column box k / 4,
+            // 32 bytes * (k % 4) along the row
+            auto issue_s = [&](int j) {
+                const uint32_t sk = skv + (j % AT_STAGES) * STAGE_BYTES;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const uint64_t dq = umma_desc(sq + (k / 4) * (AT_BM * 128)) + 2 * (k % 4);
                     const uint64_t dk = umma_desc(sk + (k / 4) * (AT_BN * 128)) + 2 * (k % 4);
-                    umma_bf16(tmem_s, dq, dk, idesc_s, k != 0);
+                    umma_bf16(tmem_s + (j & 1) * AT_BN, dq, dk, idesc_s, k != 0);
                 }
-                umma_commit(s_full);
-                ok = mbar_wait(p_ready, j & 1, a.error, 13);       // P is in shared memory (and S has been read)
+                umma_commit(s_full(j & 1));
+            };
+            bool ok = mbar_wait(q_full, 0, a.error, 12);
+            if (ok) ok = mbar_wait(kv_full(0), 0, a.error, 12);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % AT_STAGES;
+                // the scores of the NEXT tile are computed while the softmax warps work on this one
+                if (j + 1 < n_tiles) {
+                    ok = mbar_wait(kv_full((j + 1) % AT_STAGES), ((j + 1) / AT_STAGES) & 1, a.error, 12);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = mbar_wait(p_ready, j & 1, a.error, 13);       // P is in shared memory (and S of tile j has been read)
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t sv = skv + s * STAGE_BYTES + KV_BYTES;
                 // O += P V: K = 64 keys in steps of 16 (16 keys = two 8-row groups = 2048 bytes along V's rows;
                 // 32 bytes along P's rows); N = dh spans KB column boxes of V
 #pragma unroll
@@ -197,14 +212,14 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
         float m_used = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            ok = mbar_wait(s_full, j & 1, a.error, 15);
+            ok = mbar_wait(s_full(j & 1), (j >> 1) & 1, a.error, 15);
             tc_fence_after();
             if (!ok) break;
             float s[AT_BN];
             {
                 float lo[32], hi[32];
-                tmem_ld32(tmem_s + lane_sel, lo);
-                tmem_ld32(tmem_s + lane_sel + 32, hi);
+                tmem_ld32(tmem_s + (j & 1) * AT_BN + lane_sel, lo);
+                tmem_ld32(tmem_s + (j & 1) * AT_BN + lane_sel + 32, hi);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     s[i] = lo[i];
