@@ -89,30 +89,38 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
     const uint32_t sq = smem_base, sp = sq + Q_BYTES, skv = sp + P_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + Q_BYTES + P_BYTES + AT_STAGES * STAGE_BYTES);   // 2 * stages + 5
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 2 * AT_STAGES + 5);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + Q_BYTES + P_BYTES + AT_STAGES * STAGE_BYTES);   // 4 * stages + 5
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 4 * AT_STAGES + 5);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (smem_base & 1023u) {                              // never expected; refuse rather than compute garbage
         if (threadIdx.x == 0) atomicCAS(a.error, 0, 19);
         return;
     }
 
-    const int tile = a.tiles - 1 - (int)blockIdx.x;      // the tiles that see the most keys start first
-    const int h = blockIdx.y, g = h / (a.nh / a.nkvh);
+    // blocks start in the order of blockIdx.x fastest: all heads of the last tile (the one that sees the most
+    // keys) first, then all heads of the tile before it, ... : the longest jobs first over the whole grid
+    const int tile = a.tiles - 1 - (int)blockIdx.y;
+    const int h = blockIdx.x, g = h / (a.nh / a.nkvh);
     const int b = a.tile_seq[tile], t0 = a.tile_t0[tile], nq = a.tile_nq[tile];
     const int pos_first = a.tok_pos[t0], pos_last = pos_first + nq - 1;
     const int n_tiles = pos_last / AT_BN + 1;
     const int* pt = a.page_table + (size_t)b * a.max_pages;
 
     const uint32_t bar0 = smem_u32(bars);
-    auto kv_full = [&](int s) { return bar0 + 8u * s; };
-    auto kv_empty = [&](int s) { return bar0 + 8u * (AT_STAGES + s); };
-    const uint32_t q_full = bar0 + 8u * (2 * AT_STAGES), p_ready = q_full + 8, o_done = q_full + 16;
+    // K and V have barriers of their own: a K slot is free as soon as the scores that read it are done,
+    // a whole iteration before the V slot, so the next K is already on its way while P V still runs
+    auto k_full = [&](int s) { return bar0 + 8u * s; };
+    auto k_empty = [&](int s) { return bar0 + 8u * (AT_STAGES + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (2 * AT_STAGES + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (3 * AT_STAGES + s); };
+    const uint32_t q_full = bar0 + 8u * (4 * AT_STAGES), p_ready = q_full + 8, o_done = q_full + 16;
     auto s_full = [&](int i) { return q_full + 24 + 8u * i; };      // one per S buffer
     if (threadIdx.x == 0) {
         for (int s = 0; s < AT_STAGES; ++s) {
-            mbar_init(kv_full(s), 1);
-            mbar_init(kv_empty(s), 1);
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
         }
         mbar_init(q_full, 1);
         mbar_init(s_full(0), 1);
@@ -137,22 +145,26 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
             int issued = 0;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % AT_STAGES;
-                if (j >= AT_STAGES) ok = mbar_wait(kv_empty(s), ((j / AT_STAGES) - 1) & 1, a.error, 11);
-                if (!ok) break;
                 const int row = (pt[j] * a.nkvh + g) * TB_PAGE;
                 const uint32_t sk = skv + s * STAGE_BYTES, sv = sk + KV_BYTES;
-                mbar_expect_tx(kv_full(s), STAGE_BYTES);
+                if (j >= AT_STAGES) ok = mbar_wait(k_empty(s), ((j / AT_STAGES) - 1) & 1, a.error, 11);
+                if (!ok) break;
+                mbar_expect_tx(k_full(s), KV_BYTES);
 #pragma unroll
-                for (int kb = 0; kb < KB; ++kb) {
-                    tma_load_2d(sk + kb * (AT_BN * 128), &map_k, kv_full(s), kb * 64, row);
-                    tma_load_2d(sv + kb * (AT_BN * 128), &map_v, kv_full(s), kb * 64, row);
-                }
+                for (int kb = 0; kb < KB; ++kb) tma_load_2d(sk + kb * (AT_BN * 128), &map_k, k_full(s), kb * 64, row);
+                if (j >= AT_STAGES) ok = mbar_wait(v_empty(s), ((j / AT_STAGES) - 1) & 1, a.error, 11);
+                if (!ok) break;
+                mbar_expect_tx(v_full(s), KV_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) tma_load_2d(sv + kb * (AT_BN * 128), &map_v, v_full(s), kb * 64, row);
                 issued = j + 1;
             }
             if (*(volatile int*)a.error != 0) {
                 mbar_wait(q_full, 0, a.error, 14);
-                for (int j = max(0, issued - AT_STAGES); j < issued; ++j)
-                    mbar_wait(kv_full(j % AT_STAGES), (j / AT_STAGES) & 1, a.error, 14);
+                for (int j = max(0, issued - AT_STAGES); j < issued; ++j) {
+                    mbar_wait(k_full(j % AT_STAGES), (j / AT_STAGES) & 1, a.error, 14);
+                    mbar_wait(v_full(j % AT_STAGES), (j / AT_STAGES) & 1, a.error, 14);
+                }
             }
         }
     } else if (warp == 1) {
@@ -171,9 +183,10 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                     umma_bf16(tmem_s + (j & 1) * AT_BN, dq, dk, idesc_s, k != 0);
                 }
                 umma_commit(s_full(j & 1));
+                umma_commit(k_empty(j % AT_STAGES));          // K of tile j is free once these scores are done
             };
             bool ok = mbar_wait(q_full, 0, a.error, 12);
-            if (ok) ok = mbar_wait(kv_full(0), 0, a.error, 12);
+            if (ok) ok = mbar_wait(k_full(0), 0, a.error, 12);
             if (ok) {
                 tc_fence_after();
                 issue_s(0);
@@ -182,12 +195,13 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                 const int s = j % AT_STAGES;
                 // the scores of the NEXT tile are computed while the softmax warps work on this one
                 if (j + 1 < n_tiles) {
-                    ok = mbar_wait(kv_full((j + 1) % AT_STAGES), ((j + 1) / AT_STAGES) & 1, a.error, 12);
+                    ok = mbar_wait(k_full((j + 1) % AT_STAGES), ((j + 1) / AT_STAGES) & 1, a.error, 12);
                     if (!ok) break;
                     tc_fence_after();
                     issue_s(j + 1);
                 }
                 ok = mbar_wait(p_ready, j & 1, a.error, 13);       // P is in shared memory (and S of tile j has been read)
+                if (ok) ok = mbar_wait(v_full(s), (j / AT_STAGES) & 1, a.error, 12);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sv = skv + s * STAGE_BYTES + KV_BYTES;
@@ -199,7 +213,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                     const uint64_t dv = umma_desc_strides(sv + k * 2048, a.v_lbo, a.v_sbo);
                     umma_bf16(tmem_o, dp, dv, idesc_o, (j | k) != 0);
                 }
-                umma_commit(kv_empty(s));
+                umma_commit(v_empty(s));
                 umma_commit(o_done);
             }
         }
@@ -226,56 +240,65 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                     s[32 + i] = hi[i];
                 }
             }
+            // The softmax warps are bound by instruction issue and by the exponential unit, so the row is
+            // handled with as few instructions as will do: the maximum on the raw scores (the scale is
+            // positive), the mask only on tiles that reach past the row's own position, and
+            // p = 2^(s * scale - m) as one fused multiply-add and one ex2.approx each.
             const int key0 = j * AT_BN;
+            if (key0 + AT_BN - 1 > pos_first) {             // uniform over the block: a tile on or past the diagonal
+#pragma unroll
+                for (int i = 0; i < AT_BN; ++i)
+                    if (key0 + i > pos_r) s[i] = -INFINITY;
+            }
             float mx = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < AT_BN; ++i) {
-                s[i] = (key0 + i <= pos_r) ? s[i] * a.scale_log2e : -INFINITY;
-                mx = fmaxf(mx, s[i]);
-            }
+            for (int i = 0; i < AT_BN; ++i) mx = fmaxf(mx, s[i]);
+            mx *= a.scale_log2e;
             // raise the maximum only when it has grown by more than 8; then O must be rescaled
             const bool raise = mx > m_used + 8.0f;          // also true for the first visible keys (m_used = -inf)
             const float m_new = raise ? mx : m_used;
+            const float rescale = (raise && m_used != -INFINITY) ? exp2f(m_used - m_new) : 1.0f;
+            m_used = m_new;
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            // computed BEFORE waiting for the previous tile's P V: the exponentials overlap that product,
+            // only the stores below come after it
+            uint32_t pk[AT_BN / 2];
+            float psum0 = 0.f, psum1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < AT_BN; i += 2) {
+                float p0, p1;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(s[i], a.scale_log2e, neg_m)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(s[i + 1], a.scale_log2e, neg_m)));
+                psum0 += p0;
+                psum1 += p1;
+                __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1);
+                pk[i / 2] = *reinterpret_cast<uint32_t*>(&hp);
+            }
+            l_run = l_run * rescale + (psum0 + psum1);
             // the previous tile's P V must be done before P is overwritten and before O is touched
             if (j > 0) {
                 ok = mbar_wait(o_done, (j - 1) & 1, a.error, 16);
                 tc_fence_after();
                 if (!ok) break;
             }
-            if (__any_sync(0xffffffffu, raise && j > 0 && m_used != -INFINITY)) {
-                const float f = (m_used == -INFINITY) ? 1.0f : exp2f(m_used - m_new);
-                l_run *= f;
+            if (__any_sync(0xffffffffu, rescale != 1.0f) && j > 0) {
 #pragma unroll
                 for (int c0 = 0; c0 < DH; c0 += 32) {
                     float o[32];
                     tmem_ld32(tmem_o + lane_sel + c0, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] *= f;
+                    for (int i = 0; i < 32; ++i) o[i] *= rescale;
                     tmem_st32(tmem_o + lane_sel + c0, o);
                 }
-            } else if (raise && m_used != -INFINITY) {
-                l_run *= exp2f(m_used - m_new);              // j == 0 cannot get here; kept for symmetry
             }
-            m_used = m_new;
-            const float mref = (m_used == -INFINITY) ? 0.f : m_used;
-            // P = exp2(s - m) as bfloat16 into the A-operand tile [128 rows x 64 keys], 128-byte swizzle:
-            // row r at r * 128 bytes, its 16-byte chunk c at ((c ^ (r & 7)) * 16)
+            // into the A-operand tile [128 rows x 64 keys], 128-byte swizzle: row r at r * 128 bytes, its
+            // 16-byte chunk c at ((c ^ (r & 7)) * 16)
             const uint32_t prow = sp + row * 128;
 #pragma unroll
-            for (int c = 0; c < AT_BN / 8; ++c) {
-                float p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    p[i] = exp2f(s[c * 8 + i] - mref);
-                    l_run += p[i];
-                }
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0], p[1]), h1 = __floats2bfloat162_rn(p[2], p[3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(p[4], p[5]), h3 = __floats2bfloat162_rn(p[6], p[7]);
+            for (int c = 0; c < AT_BN / 8; ++c)
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((c ^ (row & 7)) << 4)),
-                             "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
-                             "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+                             "r"(pk[4 * c]), "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
                              : "memory");
-            }
             // make the generic-proxy writes of P visible to the tensor core (async proxy), then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
@@ -313,14 +336,14 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
 template <int DH>
 static int attention_tc_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AtArgs& a,
                                cudaStream_t s) {
-    const size_t smem = (size_t)AT_BM * DH * 2 + AT_BM * AT_BN * 2 + (size_t)AT_STAGES * 2 * AT_BN * DH * 2 + 128;
+    const size_t smem = (size_t)AT_BM * DH * 2 + AT_BM * AT_BN * 2 + (size_t)AT_STAGES * 2 * AT_BN * DH * 2 + 160;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(a.tiles, a.nh);
+    dim3 grid(a.nh, a.tiles);
     TB_LAUNCH((attention_tc_kernel<DH>), grid, AT_THREADS, smem, s, mq, mk, mv, a);
     return tb_last_error();
 }
