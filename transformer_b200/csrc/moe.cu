@@ -82,18 +82,19 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
     for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] *= inv;
 }
 
-// Top-k and weights from router logits that are already in memory (float [nt, E]): one warp per token.
+// Top-k and weights from router logits that are already in memory: one warp per token.  The logit of
+// (token t, expert e) is at logits[t * ld_t + e * ld_e], so both [nt, E] and [E, nt] layouts serve.
 // Same rules as router_kernel; used when the logits come from a matrix-product kernel.
 __global__ void __launch_bounds__(128)
-topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx, float* __restrict__ topk_w, int nt,
-                    int E, int k) {
+topk_softmax_kernel(const float* __restrict__ logits, long long ld_t, long long ld_e, int* __restrict__ topk_idx,
+                    float* __restrict__ topk_w, int nt, int E, int k) {
     pdl_sync();
     extern __shared__ float lg_all[];   // [4][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 4 + warp;
     if (t >= nt) return;
     float* lg = lg_all + warp * E;
-    for (int e = lane; e < E; e += 32) lg[e] = logits[(size_t)t * E + e];
+    for (int e = lane; e < E; e += 32) lg[e] = logits[(size_t)t * ld_t + (size_t)e * ld_e];
     __syncwarp();
     float v0 = 0.f, sum = 0.f;
     for (int j = 0; j < k; ++j) {
@@ -209,11 +210,12 @@ int tb_router_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w,
                    int E, int k, cudaStream_t s) {
     return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k, s);
 }
-int tb_topk_softmax(const float* logits, int* topk_idx, float* topk_w, int nt, int E, int k, cudaStream_t s) {
+int tb_topk_softmax(const float* logits, long long ld_t, long long ld_e, int* topk_idx, float* topk_w, int nt, int E, int k,
+                    cudaStream_t s) {
     if (nt < 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
     if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
-    TB_LAUNCH((topk_softmax_kernel), (nt + 3) / 4, 128, (size_t)4 * E * sizeof(float), s, logits, topk_idx, topk_w, nt, E, k);
+    TB_LAUNCH((topk_softmax_kernel), (nt + 3) / 4, 128, (size_t)4 * E * sizeof(float), s, logits, ld_t, ld_e, topk_idx, topk_w, nt, E, k);
     return tb_last_error();
 }
 int tb_moe_dispatch(const int* topk_idx, int* group_offsets, int* sorted_token, int* pair_row, int M, int k, int E,

@@ -11,7 +11,7 @@ import torch
 
 from ..csrc import lib
 from .base import FEED_FORWARDS, FeedForward, ParamDecl, WeightedRows
-from .linear import gemm_tc, grouped_matmul, matmul_nt
+from .linear import gemm_skinny, grouped_matmul, matmul_nt
 
 ROUTER_PRODUCT_ROWS = 256   # above this many tokens the router logits come from the prompt product kernel
 
@@ -66,12 +66,13 @@ class MoE(FeedForward):
         nt = x1.shape[0]
         idx = ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32)
         w = ctx.scratch("moe.topk_w", (nt, self.k), torch.float32)
-        if self.dtype == torch.bfloat16 and nt > ROUTER_PRODUCT_ROWS:
-            # many tokens: the logits are a matrix product (tensor cores, float accumulation and output),
-            # then one small kernel picks the experts
-            lg = logits_out if logits_out is not None else ctx.scratch("moe.logits", (nt, self.E), torch.float32)
-            if gemm_tc(x1, self.weights["router"], lg, out_kind=1):
-                lib.call("tb_topk_softmax", lib.ptr(lg), lib.ptr(idx), lib.ptr(w), nt, self.E, self.k)
+        if self.dtype == torch.bfloat16 and nt > ROUTER_PRODUCT_ROWS and logits_out is None and self.E <= 64:
+            # many tokens, few experts: the logits are a product whose long operand is the ACTIVATIONS, so the
+            # decode product kernel streams x1 once with the roles swapped (experts as its few "tokens"),
+            # float accumulation and output [E, nt]; one small kernel then picks the experts
+            lg = ctx.scratch("moe.logits", (self.E, nt), torch.float32)
+            if gemm_skinny(self.weights["router"], x1, lg, out_kind=1):
+                lib.call("tb_topk_softmax", lib.ptr(lg), 1, nt, lib.ptr(idx), lib.ptr(w), nt, self.E, self.k)
                 return idx, w
         lib.call("tb_router_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
                  lib.ptr(idx), lib.ptr(w), lib.ptr(logits_out), nt, self.d, self.E, self.k)
