@@ -102,13 +102,20 @@ def test_rope_and_cache_write(dtype, pairing):
 
 
 # ---------------------------------------------------------------------------------------------
-def _run_attention(lib, c, dtype, splits, decode):
+def _run_attention(lib, c, dtype, splits, decode, tma=False):
     nt, nh, dh = c["nt"], c["nh"], c["dh"]
     out = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
     partial = torch.empty(max(1, nt * nh * splits * (dh + 2)), dtype=torch.float32, device="cuda")
     scale = 1.0 / math.sqrt(dh)
     if decode:
         seq = torch.repeat_interleave(c["tile_seq"], c["tile_nq"])
+        if tma:
+            ok = lib.try_call("tb_attention_decode_tma_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
+                              c["vc"].data_ptr(), seq.data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(),
+                              partial.data_ptr(), nt, c["max_pages"], nh * dh, nh, c["nkvh"], dh, splits,
+                              c["kc"].shape[0], scale)
+            assert lib.gemm_tc_status() == 0
+            return out.double().cpu().reshape(nt, nh, dh) if ok else None
         ok = lib.try_call("tb_attention_decode_" + lib.suffix(dtype), c["q"].data_ptr(), out.data_ptr(),
                           c["kc"].data_ptr(), c["vc"].data_ptr(), seq.data_ptr(), c["tok_pos"].data_ptr(),
                           c["table"].data_ptr(), partial.data_ptr(), nt, c["max_pages"], nh * dh, nh, c["nkvh"], dh,
@@ -418,3 +425,17 @@ def test_attention_tcgen05_kernel(nh, nkvh, dh):
     assert lib.gemm_tc_status() == 0, "a wait inside the kernel gave up"
     got = out.double().cpu().reshape(nt, nh, dh)
     assert float((got - c["ref"]).abs().max()) <= _tol(dtype, 4.0)
+
+
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 64), (8, 8, 128), (12, 2, 64), (20, 2, 128), (3, 1, 128)])
+def test_attention_decode_tma(nh, nkvh, dh):
+    """The TMA-fed decode kernel: contexts of one token, exactly one page, a page and a bit, many pages;
+    key slices that leave some slices empty."""
+    lib = _lib()
+    c = attention_case([1, 1, 1, 1, 1], [0, 63, 64, 700, 129], nh, nkvh, dh, torch.bfloat16, 1, seed=5 * nh + dh)
+    for splits in (1, 2, 7):
+        got = _run_attention(lib, c, torch.bfloat16, splits, decode=True, tma=True)
+        assert got is not None
+        assert float((got - c["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"splits {splits}"
+    c48 = attention_case([1], [10], 2, 1, 48, torch.bfloat16, 1, seed=1)
+    assert _run_attention(lib, c48, torch.bfloat16, 1, decode=True, tma=True) is None, "a head of 48 is refused"

@@ -7,6 +7,7 @@
 //  * every launcher is `extern "C"`, takes raw device pointers, sizes and a cudaStream_t, checks
 //    its sizes, and returns 0 or a cudaError_t / negative argument error; it never allocates.
 #pragma once
+#include <mutex>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -129,9 +130,47 @@ __device__ __forceinline__ void pdl_sync() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// Every kernel states how much of the SM's unified L1/shared memory it wants as shared memory: what the
+// blocks that fit by threads and registers need together, and no more.  Without the statement the split
+// that a kernel with a large ring asked for stays in force, and the kernels after it run with a sliver
+// of L1 (measured: a decode step of small kernels lost a third of its speed behind one 200 KB kernel).
+// Looked up per kernel, set again only when a launch needs more than any before it.
+static inline void tb_state_carveout(const void* kernel, unsigned threads, size_t dyn_smem) {
+    struct Seen { const void* kernel; size_t need; };
+    static Seen seen[128];
+    static int n_seen = 0;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> hold(lock);
+    int at = -1;
+    for (int i = 0; i < n_seen; ++i)
+        if (seen[i].kernel == kernel) { at = i; break; }
+    if (at >= 0 && dyn_smem <= seen[at].need) return;
+    if (at < 0) {
+        if (n_seen == 128) return;
+        at = n_seen++;
+        seen[at].kernel = kernel;
+    }
+    seen[at].need = dyn_smem;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) { cudaGetLastError(); return; }
+    const unsigned warps = (threads + 31) / 32;
+    const unsigned regs_per_warp = ((unsigned)fa.numRegs * 32 + 255) / 256 * 256;
+    unsigned blocks = 2048 / (warps * 32);
+    if (regs_per_warp) blocks = blocks < 65536 / (regs_per_warp * warps) ? blocks : 65536 / (regs_per_warp * warps);
+    if (blocks > 32) blocks = 32;
+    if (blocks < 1) blocks = 1;
+    const size_t per_block = fa.sharedSizeBytes + dyn_smem + 1024, sm_total = 228 * 1024;
+    size_t want = blocks * per_block;
+    if (want > sm_total) want = sm_total / per_block ? sm_total / per_block * per_block : per_block;
+    int pct = (int)((want * 100 + sm_total - 1) / sm_total);
+    pct = pct < 12 ? 12 : pct > 100 ? 100 : pct;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, pct) != cudaSuccess) cudaGetLastError();
+}
+
 template <typename... KArgs, typename... Args>
 static inline void tb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args... args) {
+    tb_state_carveout((const void*)kernel, block.x * block.y * block.z, smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

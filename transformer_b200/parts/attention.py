@@ -17,6 +17,7 @@ from .spec import PartSpec
 
 
 USE_TCGEN05 = True     # prompts: the tcgen05 kernel before the mma.sync one
+USE_DECODE_TMA = True  # decoding: cache pages by TMA before the register-staged kernel
 
 
 @MIXERS.register("attention")
@@ -110,6 +111,12 @@ class Attention(Mixer):
         partial = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
+        if USE_DECODE_TMA and self.dtype == torch.bfloat16 and self.dh in (64, 128) and \
+                lib.try_call("tb_attention_decode_tma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                             lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
+                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, cache.k.shape[0],
+                             self.scale):
+            return True
         return lib.try_call("tb_attention_decode_" + sfx, lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                             lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, self.scale)
