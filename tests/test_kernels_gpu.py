@@ -112,8 +112,7 @@ def _run_attention(lib, c, dtype, splits, decode, tma=False):
         if tma:
             ok = lib.try_call("tb_attention_decode_tma_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
                               c["vc"].data_ptr(), seq.data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(),
-                              partial.data_ptr(), nt, c["max_pages"], nh * dh, nh, c["nkvh"], dh, splits,
-                              c["kc"].shape[0], scale)
+                              partial.data_ptr(), nt, c["max_pages"], nh * dh, nh, c["nkvh"], dh, splits, scale)
             assert lib.gemm_tc_status() == 0
             return out.double().cpu().reshape(nt, nh, dh) if ok else None
         ok = lib.try_call("tb_attention_decode_" + lib.suffix(dtype), c["q"].data_ptr(), out.data_ptr(),

@@ -58,8 +58,9 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(const Deco
     const int split = blockIdx.z;
     const int b = a.tok_seq[t], pos = a.tok_pos[t];
     const int n_keys = pos + 1;
-    int per = (n_keys + a.splits - 1) / a.splits;
-    per = (per + TB_PAGE - 1) / TB_PAGE * TB_PAGE;
+    const int n_pages = pos / TB_PAGE + 1, slices = decode_slices(n_pages, a.splits);
+    if (split >= slices) return;
+    const int per = (n_pages + slices - 1) / slices * TB_PAGE;
     const int k_lo = split * per, k_hi = min(n_keys, k_lo + per);
 
     const T* qg = static_cast<const T*>(a.q) + (size_t)t * a.q_stride + (size_t)h0 * dh + li * EPL;
@@ -233,7 +234,8 @@ static int decode_launch(const DecodeArgs& a, int nt, cudaStream_t s) {
     if (rc) return rc;
     if (a.splits > 1) {
         dim3 grid(nt, a.nh);
-        TB_LAUNCH((attention_merge_kernel<T>), grid, a.dh < 128 ? 64 : 128, 0, s, a.partial, (T*)a.out, a.nh, a.dh, a.splits);
+        TB_LAUNCH((attention_merge_kernel<T>), grid, a.dh < 128 ? 64 : 128, 0, s, a.partial, (T*)a.out, a.nh, a.dh, a.splits,
+                  a.tok_pos);
         rc = tb_last_error();
     }
     return rc;

@@ -19,6 +19,8 @@
 
 struct DecodeTmaArgs {
     const __nv_bfloat16* q;   // [nt, q_stride]
+    const __nv_bfloat16* kc;  // [pages, nkvh, TB_PAGE, dh]
+    const __nv_bfloat16* vc;
     __nv_bfloat16* out;       // [nt, nh * dh]
     const int* tok_seq;
     const int* tok_pos;
@@ -30,11 +32,11 @@ struct DecodeTmaArgs {
 };
 
 template <int DH, int GC>
-__global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
-                                                                         const __grid_constant__ CUtensorMap map_v,
-                                                                         const DecodeTmaArgs a) {
-    pdl_sync();
-    constexpr int KB = DH / 64;                         // 64-column boxes per row
+__global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const DecodeTmaArgs a) {
+    // The next kernel may start launching at once.  This one waits for the kernel before it (which wrote the
+    // step's queries and the newest key and value) as late as it can: page numbers, positions and every cache
+    // page but the sequence's last were written before the step began, so the ring is filled meanwhile.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int TPK = DH / 8;                         // lanes per key (8 or 16)
     constexpr int NSW = DT_WARPS * 32 / TPK;            // sub-warps among the arithmetic warps
     constexpr int KPS = TB_PAGE / NSW;                  // keys of a page per sub-warp (4 or 8)
@@ -58,7 +60,9 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
     const int split = blockIdx.z;
     const int b = a.tok_seq[t], pos = a.tok_pos[t];
     const int n_pages = pos / TB_PAGE + 1;
-    const int per = (n_pages + a.splits - 1) / a.splits;
+    const int slices = decode_slices(n_pages, a.splits);
+    if (split >= slices) return;
+    const int per = (n_pages + slices - 1) / slices;
     const int p_lo = split * per, p_hi = min(n_pages, p_lo + per);
     const int np = max(0, p_hi - p_lo);
     const int* pt = a.page_table + (size_t)b * a.max_pages;
@@ -77,33 +81,39 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
     __syncthreads();
 
     if (warp == DT_WARPS) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            bool ok = true;
-            int issued = 0;
-            for (int i = 0; i < np && ok; ++i) {
-                const int s = i % S;
+        // ---------------- producer: the whole warp reads page numbers, lane 0 asks for the copies ----------------
+        bool ok = true, waited = false;
+        int issued = 0, mine = 0;
+        for (int i = 0; i < np && ok; ++i) {
+            if ((i & 31) == 0) mine = (i + lane < np) ? pt[p_lo + i + lane] : 0;
+            const int page = __shfl_sync(0xffffffffu, mine, i & 31);
+            const int s = i % S;
+            if (lane == 0) {
                 if (i >= S) ok = mbar_wait(empty_bar(s), ((i / S) - 1) & 1, a.error, 21);
-                if (!ok) break;
-                const int row = (pt[p_lo + i] * a.nkvh + g) * TB_PAGE;
-                const uint32_t sk = smem_base + s * STAGE_BYTES, sv = sk + PAGE_BYTES;
-                mbar_expect_tx(full_bar(s), STAGE_BYTES);
-#pragma unroll
-                for (int kb = 0; kb < KB; ++kb) {
-                    tma_load_2d(sk + kb * (TB_PAGE * 128), &map_k, full_bar(s), kb * 64, row);
-                    tma_load_2d(sv + kb * (TB_PAGE * 128), &map_v, full_bar(s), kb * 64, row);
+                if (ok) {
+                    if (!waited && p_lo + i == n_pages - 1) {   // the page the kernel before this one wrote to
+                        asm volatile("griddepcontrol.wait;" ::: "memory");
+                        waited = true;
+                    }
+                    // one head's keys of a page are TB_PAGE * DH contiguous elements of the cache
+                    const size_t at = ((size_t)page * a.nkvh + g) * (TB_PAGE * DH);
+                    const uint32_t sk = smem_base + s * STAGE_BYTES, sv = sk + PAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    bulk_load(sk, a.kc + at, PAGE_BYTES, full_bar(s));
+                    bulk_load(sv, a.vc + at, PAGE_BYTES, full_bar(s));
+                    issued = i + 1;
                 }
-                issued = i + 1;
             }
-            if (*(volatile int*)a.error != 0)
-                for (int i = max(0, issued - S); i < issued; ++i) mbar_wait(full_bar(i % S), (i / S) & 1, a.error, 24);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
+        if (lane == 0 && *(volatile int*)a.error != 0)
+            for (int i = max(0, issued - S); i < issued; ++i) mbar_wait(full_bar(i % S), (i / S) & 1, a.error, 24);
     } else {
         // ---------------- arithmetic warps ----------------
         const int tid = threadIdx.x;                 // 0 .. 127
         const int sw = tid / TPK, li = tid % TPK;    // sub-warp, lane in it: channels li * 8 .. + 8
-        const int box = li / 8, chunk = li % 8;      // which 64-column box, which 16-byte chunk of its 128-byte row
         float q[GC][8], o[GC][8], m[GC], l[GC];
+        asm volatile("griddepcontrol.wait;" ::: "memory");     // the queries come from the kernel before
         const __nv_bfloat16* qg = a.q + (size_t)t * a.q_stride + (size_t)h0 * DH + li * 8;
 #pragma unroll
         for (int hc = 0; hc < GC; ++hc) {
@@ -122,11 +132,11 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
             const int s = i % S;
             ok = mbar_wait(full_bar(s), (i / S) & 1, a.error, 22);
             if (!ok) break;
-            const uint8_t* sk = smem_al + (size_t)s * STAGE_BYTES + box * (TB_PAGE * 128);
+            const uint8_t* sk = smem_al + (size_t)s * STAGE_BYTES + li * 16;
             const uint8_t* sv = sk + PAGE_BYTES;
             const int key0 = (p_lo + i) * TB_PAGE;
-            // this sub-warp's keys of the page: r = sw, sw + NSW, ..., four at a time; row r of the box at
-            // r * 128 bytes, its 16-byte chunk c at ((c ^ (r & 7)) * 16) (the swizzle TMA wrote)
+            // this sub-warp's keys of the page: r = sw, sw + NSW, ..., four at a time; a quarter-warp reads
+            // 128 contiguous bytes, so the plain row-major page has no bank conflicts
 #pragma unroll
             for (int u0 = 0; u0 < KPS; u0 += KU) {
                 float kf[KU][8], vf[KU][8];
@@ -134,7 +144,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
 #pragma unroll
                 for (int u = 0; u < KU; ++u) {
                     const int r = sw + (u0 + u) * NSW;
-                    const int off = r * 128 + ((chunk ^ (r & 7)) << 4);
+                    const int off = r * (DH * 2);
                     live[u] = key0 + r <= pos;
                     Vec16<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(sk + off), kf[u]);
                     Vec16<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(sv + off), vf[u]);
@@ -223,7 +233,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
 }
 
 template <int DH, int GC>
-static int decode_tma_launch(const CUtensorMap& mk, const CUtensorMap& mv, DecodeTmaArgs a, int nt, cudaStream_t s) {
+static int decode_tma_launch(DecodeTmaArgs a, int nt, cudaStream_t s) {
     constexpr int NSW = DT_WARPS * 32 / (DH / 8);
     const size_t stage = (size_t)2 * TB_PAGE * DH * 2;
     const size_t tail = 2 * DT_MAX_STAGES * 8 + (size_t)(NSW * GC * DH + 2 * NSW * GC) * sizeof(float);
@@ -242,42 +252,37 @@ static int decode_tma_launch(const CUtensorMap& mk, const CUtensorMap& mv, Decod
     }
     const int group = a.nh / a.nkvh;
     dim3 grid(nt, a.nkvh * ((group + GC - 1) / GC), a.splits);
-    TB_LAUNCH((attention_decode_tma_kernel<DH, GC>), grid, DT_THREADS, smem, s, mk, mv, a);
+    TB_LAUNCH((attention_decode_tma_kernel<DH, GC>), grid, DT_THREADS, smem, s, a);
     return tb_last_error();
 }
 
 extern "C" int tb_attention_decode_tma_bf16(const void* q, void* out, const void* kc, const void* vc, const int* tok_seq,
                                             const int* tok_pos, const int* page_table, float* partial, int nt,
                                             int max_pages, int q_stride, int nh, int nkvh, int dh, int splits,
-                                            int cache_pages, float scale, cudaStream_t s) {
-    if (nh <= 0 || nkvh <= 0 || nh % nkvh || splits < 1 || cache_pages <= 0) return TB_ERR_ARG;
+                                            float scale, cudaStream_t s) {
+    if (nh <= 0 || nkvh <= 0 || nh % nkvh || splits < 1) return TB_ERR_ARG;
     if (splits > 1 && !partial) return TB_ERR_ARG;
     if (dh != 64 && dh != 128) return TB_ERR_UNSUPPORTED;
     if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) & 15)) return TB_ERR_UNSUPPORTED;
     if (nt <= 0) return nt == 0 ? 0 : TB_ERR_ARG;
-    CUtensorMap mk, mv;
-    const long long rows = (long long)cache_pages * nkvh * TB_PAGE;
-    int rc = make_map(&mk, kc, rows, dh, dh, TB_PAGE);
-    if (rc) return rc;
-    rc = make_map(&mv, vc, rows, dh, dh, TB_PAGE);
-    if (rc) return rc;
+    int rc = 0;
     int* err = tc_error_ptr();
     if (!err) return TB_ERR_UNSUPPORTED;
-    DecodeTmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_seq, tok_pos, page_table, partial, err,
+    DecodeTmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, tok_seq, tok_pos, page_table, partial, err,
                     max_pages, q_stride, nh, nkvh, splits, 0, scale * 1.4426950408889634f};
     const int group = nh / nkvh;
     const int gc = group == 1 ? 1 : group == 2 ? 2 : 4;
     if (dh == 64)
-        rc = gc == 1 ? decode_tma_launch<64, 1>(mk, mv, a, nt, s)
-                     : gc == 2 ? decode_tma_launch<64, 2>(mk, mv, a, nt, s) : decode_tma_launch<64, 4>(mk, mv, a, nt, s);
+        rc = gc == 1 ? decode_tma_launch<64, 1>(a, nt, s)
+                     : gc == 2 ? decode_tma_launch<64, 2>(a, nt, s) : decode_tma_launch<64, 4>(a, nt, s);
     else
-        rc = gc == 1 ? decode_tma_launch<128, 1>(mk, mv, a, nt, s)
-                     : gc == 2 ? decode_tma_launch<128, 2>(mk, mv, a, nt, s) : decode_tma_launch<128, 4>(mk, mv, a, nt, s);
+        rc = gc == 1 ? decode_tma_launch<128, 1>(a, nt, s)
+                     : gc == 2 ? decode_tma_launch<128, 2>(a, nt, s) : decode_tma_launch<128, 4>(a, nt, s);
     if (rc) return rc;
     if (splits > 1) {
         dim3 grid(nt, nh);
         TB_LAUNCH((attention_merge_kernel<__nv_bfloat16>), grid, dh < 128 ? 64 : 128, 0, s, partial,
-                  (__nv_bfloat16*)out, nh, dh, splits);
+                  (__nv_bfloat16*)out, nh, dh, splits, tok_pos);
         rc = tb_last_error();
     }
     return rc;

@@ -155,13 +155,23 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_kernel(const AttnArg
     }
 }
 
-// out[t, h, :] = sum_s o_s exp(m_s - m) / sum_s l_s exp(m_s - m),  m = max_s m_s
+// Slices into which a decode kernel cuts a sequence of n_pages pages: at most `splits` (the depth of its grid,
+// a function of the batch's shape alone so that a captured graph can keep it) and none shorter than two pages.
+// The kernels and the merge agree through this one function; blocks of slices beyond it write nothing.
+__host__ __device__ inline int decode_slices(int n_pages, int splits) {
+    const int s = n_pages / 2;
+    return s < 1 ? 1 : s > splits ? splits : s;
+}
+
+// out[t, h, :] = sum_s o_s exp(m_s - m) / sum_s l_s exp(m_s - m),  m = max_s m_s.
+// tok_pos (decoding) limits the sum to the slices that the token's sequence was cut into.
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int nh, int dh,
-                                       int splits) {
+                                       int splits, const int* __restrict__ tok_pos) {
     pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const float* p = partial + ((size_t)t * nh + h) * splits * (dh + 2);
+    if (tok_pos) splits = decode_slices(tok_pos[t] / TB_PAGE + 1, splits);
     float m = -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, p[s * (dh + 2) + dh]);
     float den = 0.f;
@@ -223,7 +233,8 @@ static int attention_launch(AttnArgs a, int tiles, int nt, cudaStream_t s) {
     if (rc) return rc;
     if (a.splits > 1) {
         dim3 grid(nt, a.nh);
-        TB_LAUNCH((attention_merge_kernel<T>), grid, a.dh < 128 ? 64 : 128, 0, s, a.partial, (T*)a.out, a.nh, a.dh, a.splits);
+        TB_LAUNCH((attention_merge_kernel<T>), grid, a.dh < 128 ? 64 : 128, 0, s, a.partial, (T*)a.out, a.nh, a.dh, a.splits,
+                  (const int*)nullptr);
         rc = tb_last_error();
     }
     return rc;

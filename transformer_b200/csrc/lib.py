@@ -33,7 +33,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_attention_prefill_bf16": "pppppppppiiiiiif",
     "tb_attention_tc_bf16": "pppppppppiiiiiiiifii",
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
-    "tb_attention_decode_tma_bf16": "ppppppppiiiiiiiif",
+    "tb_attention_decode_tma_bf16": "ppppppppiiiiiiif",
     "tb_router_f32": "pppppiiii", "tb_router_bf16": "pppppiiii",
     "tb_moe_dispatch": "ppppiii", "tb_topk_softmax": "pllppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",

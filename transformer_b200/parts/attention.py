@@ -106,16 +106,16 @@ class Attention(Mixer):
         group = self.nh // self.nkvh
         gc = 1 if group == 1 else 2 if group == 2 else 4
         blocks = nt * self.nkvh * ((group + gc - 1) // gc)
-        # enough blocks to fill the GPU eight times over, but no slice shorter than 128 keys of the longest sequence
-        splits = int(max(1, min(32, (8 * ctx.engine.sm_count) // blocks, ctx.max_len_after // 128)))
+        # enough blocks to fill the GPU eight times over; a function of the batch's shape alone, since a captured
+        # graph keeps it for as long as the sequences grow (a slice that a short sequence leaves empty costs little)
+        splits = int(max(1, min(32, (8 * ctx.engine.sm_count) // blocks)))
         partial = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
         if USE_DECODE_TMA and self.dtype == torch.bfloat16 and self.dh in (64, 128) and \
                 lib.try_call("tb_attention_decode_tma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                              lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
-                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, cache.k.shape[0],
-                             self.scale):
+                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, self.scale):
             return True
         return lib.try_call("tb_attention_decode_" + sfx, lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                             lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
