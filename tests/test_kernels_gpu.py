@@ -102,7 +102,7 @@ def test_rope_and_cache_write(dtype, pairing):
 
 
 # ---------------------------------------------------------------------------------------------
-def _run_attention(lib, c, dtype, splits, decode, tma=False):
+def _run_attention(lib, c, dtype, splits, decode, tma=False, done=None):
     nt, nh, dh = c["nt"], c["nh"], c["dh"]
     out = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
     partial = torch.empty(max(1, nt * nh * splits * (dh + 2)), dtype=torch.float32, device="cuda")
@@ -112,7 +112,8 @@ def _run_attention(lib, c, dtype, splits, decode, tma=False):
         if tma:
             ok = lib.try_call("tb_attention_decode_tma_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
                               c["vc"].data_ptr(), seq.data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(),
-                              partial.data_ptr(), nt, c["max_pages"], nh * dh, nh, c["nkvh"], dh, splits, scale)
+                              partial.data_ptr(), 0 if done is None else done.data_ptr(), nt, c["max_pages"], nh * dh,
+                              nh, c["nkvh"], dh, splits, scale)
             assert lib.gemm_tc_status() == 0
             return out.double().cpu().reshape(nt, nh, dh) if ok else None
         ok = lib.try_call("tb_attention_decode_" + lib.suffix(dtype), c["q"].data_ptr(), out.data_ptr(),
@@ -196,7 +197,8 @@ def _grouped_case(dtype, E, k, nt, d, di, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("E,k,nt,d,di", [(4, 2, 9, 64, 40), (16, 4, 8, 256, 86), (6, 3, 200, 96, 80), (3, 3, 1, 72, 16)])
+@pytest.mark.parametrize("E,k,nt,d,di", [(4, 2, 9, 64, 40), (16, 4, 8, 256, 86), (6, 3, 200, 96, 80), (3, 3, 1, 72, 16),
+                                          (16, 4, 64, 128, 88), (5, 2, 13, 2048, 48)])
 def test_dispatch_grouped_products_and_combine(dtype, E, k, nt, d, di):
     """token -> expert dispatch, the grouped gate/up product with swiglu, the grouped down product
     and the weighted combine, against a per-token loop."""
@@ -219,17 +221,26 @@ def test_dispatch_grouped_products_and_combine(dtype, E, k, nt, d, di):
         for j in range(k):
             e = int(idx[t, j])
             ref[t] += float(w[t, j]) * P.expert_ffn(x[t].double().cpu(), wgu[e].double().cpu(), wd[e].double().cpu())
-    for use in ("auto", "simt"):
+    uses = ("auto", "simt") + (("unsorted",) if dtype == torch.bfloat16 and M <= 256 and d % 8 == 0 and di % 8 == 0 else ())
+    for use in uses:
         h = torch.empty((M, di), dtype=dtype, device="cuda")
         y = torch.empty((M, d), dtype=dtype, device="cuda")
-        if use == "auto":
+        rows = pr
+        if use == "unsorted":
+            # no lists: row p is pair p, and every block picks its expert's pairs out of the router's answer
+            from transformer_b200.parts.linear import gemm_skinny
+            pairs = idx.view(-1)
+            assert gemm_skinny(x, wgu, h, groups=E, out_kind=2, max_group_rows=nt, row_group=pairs, x_div=k)
+            assert gemm_skinny(h, wd, y, groups=E, max_group_rows=nt, row_group=pairs)
+            rows = torch.arange(M, dtype=torch.int32, device="cuda")
+        elif use == "auto":
             grouped_matmul(x, wgu, h, a_rows=st, group_offsets=off, groups=E, swiglu=True)
             grouped_matmul(h, wd, y, group_offsets=off, groups=E)
         else:
             gemm_simt(x, wgu, h, a_rows=st, group_offsets=off, groups=E, out_kind=2)
             gemm_simt(h, wd, y, group_offsets=off, groups=E, out_kind=0)
         out = torch.empty((nt, d), dtype=dtype, device="cuda")
-        lib.call("tb_moe_combine_" + lib.suffix(dtype), y.data_ptr(), pr.data_ptr(), w.data_ptr(), out.data_ptr(),
+        lib.call("tb_moe_combine_" + lib.suffix(dtype), y.data_ptr(), rows.data_ptr(), w.data_ptr(), out.data_ptr(),
                  nt, d, k)
         assert float((out.double().cpu() - ref).abs().max()) <= 2 * _tol(dtype, float(ref.abs().max())), use
 
@@ -259,7 +270,26 @@ def test_router(dtype, E, k, d, nt):
     w = torch.empty((nt, k), dtype=torch.float32, device="cuda")
     lg = torch.empty((nt, E), dtype=torch.float32, device="cuda")
     lib.call("tb_router_" + lib.suffix(dtype), x.data_ptr(), wr.data_ptr(), idx.data_ptr(), w.data_ptr(),
-             lg.data_ptr(), nt, d, E, k)
+             lg.data_ptr(), 0, 0, 0, 0, nt, d, E, k)
+    # the same kernel with the dispatch lists built by its last block, twice (the counter is left at zero)
+    offs = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    tok = torch.empty(nt * k, dtype=torch.int32, device="cuda")
+    row = torch.empty(nt * k, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    idx2, w2 = torch.empty_like(idx), torch.empty_like(w)
+    for _ in range(2):
+        offs.fill_(-1), tok.fill_(-1), row.fill_(-1)
+        lib.call("tb_router_" + lib.suffix(dtype), x.data_ptr(), wr.data_ptr(), idx2.data_ptr(), w2.data_ptr(), 0,
+                 offs.data_ptr(), tok.data_ptr(), row.data_ptr(), done.data_ptr(), nt, d, E, k)
+        assert torch.equal(idx2, idx) and torch.equal(w2, w) and int(done) == 0
+        flat = idx.flatten().cpu()
+        counts = torch.bincount(flat, minlength=E)
+        assert offs.cpu().tolist() == [0] + torch.cumsum(counts, 0).tolist()
+        r = row.cpu().long()
+        assert sorted(r.tolist()) == list(range(nt * k)), "every pair has a row of its own"
+        assert torch.equal(tok.cpu()[r], torch.arange(nt * k, dtype=torch.int32) // k), "a row reads its pair's token"
+        e_of_row = torch.bucketize(r, offs.cpu().long()[1:], right=True)
+        assert torch.equal(e_of_row, flat.long()), "a pair's row lies in its expert's range"
     ref_lg = x.double() @ wr.double().T
     assert float((lg.double() - ref_lg).abs().max()) <= 2e-5 * max(1.0, float(ref_lg.abs().max())), \
         "router logits are float whatever the storage type"
@@ -277,7 +307,7 @@ def test_router_ties_go_to_the_lower_expert():
     wr[[1, 4, 6, 7]] = 0.5                                  # four equal best logits
     idx = torch.empty((1, k), dtype=torch.int32, device="cuda")
     w = torch.empty((1, k), dtype=torch.float32, device="cuda")
-    lib.call("tb_router_f32", x.data_ptr(), wr.data_ptr(), idx.data_ptr(), w.data_ptr(), 0, 1, d, E, k)
+    lib.call("tb_router_f32", x.data_ptr(), wr.data_ptr(), idx.data_ptr(), w.data_ptr(), 0, 0, 0, 0, 0, 1, d, E, k)
     assert idx[0].tolist() == [1, 4, 6] and torch.allclose(w, torch.full_like(w, 1 / 3))
 
 
@@ -433,8 +463,11 @@ def test_attention_decode_tma(nh, nkvh, dh):
     lib = _lib()
     c = attention_case([1, 1, 1, 1, 1], [0, 63, 64, 700, 129], nh, nkvh, dh, torch.bfloat16, 1, seed=5 * nh + dh)
     for splits in (1, 2, 7):
-        got = _run_attention(lib, c, torch.bfloat16, splits, decode=True, tma=True)
-        assert got is not None
-        assert float((got - c["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"splits {splits}"
+        done = torch.zeros(5 * nh, dtype=torch.int32, device="cuda")
+        for counters in (None, done, done):     # a merge kernel; the last block merges (twice: counters left at zero)
+            got = _run_attention(lib, c, torch.bfloat16, splits, decode=True, tma=True, done=counters)
+            assert got is not None
+            assert float((got - c["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"splits {splits}"
+            assert int(done.abs().sum()) == 0
     c48 = attention_case([1], [10], 2, 1, 48, torch.bfloat16, 1, seed=1)
     assert _run_attention(lib, c48, torch.bfloat16, 1, decode=True, tma=True) is None, "a head of 48 is refused"

@@ -26,6 +26,7 @@ struct DecodeTmaArgs {
     const int* tok_pos;
     const int* page_table;
     float* partial;           // [nt, nh, splits, dh + 2] when splits > 1
+    unsigned* done;           // [nt, gridDim.y] zeroed counters of finished slices (left zeroed), or null
     int* error;
     int max_pages, q_stride, nh, nkvh, splits, stages;
     float scale_log2e;
@@ -230,6 +231,34 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
             }
         }
     }
+    if (a.splits == 1 || !a.done) return;
+    // The block that finishes a (token, head group)'s last slice merges the slices: no kernel of its own for it.
+    __shared__ bool last_slice;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* count = a.done + (size_t)t * gridDim.y + blockIdx.y;
+        last_slice = atomicAdd(count, 1u) == (unsigned)slices - 1;
+        if (last_slice) *count = 0;
+    }
+    __syncthreads();
+    if (!last_slice) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < nheads * DH; idx += DT_THREADS) {
+        const int hc = idx / DH, c = idx - hc * DH, h = h0 + hc;
+        const float* p = a.partial + ((size_t)t * a.nh + h) * a.splits * (DH + 2);
+        float mx = -INFINITY;
+        for (int s = 0; s < slices; ++s) mx = fmaxf(mx, __ldcg(p + s * (DH + 2) + DH));
+        float den = 0.f, acc = 0.f;
+        for (int s = 0; s < slices; ++s) {
+            const float ms = __ldcg(p + s * (DH + 2) + DH);
+            if (ms == -INFINITY) continue;
+            const float w = expf(ms - mx);
+            den += __ldcg(p + s * (DH + 2) + DH + 1) * w;
+            acc += __ldcg(p + s * (DH + 2) + c) * w;
+        }
+        a.out[((size_t)t * a.nh + h) * DH + c] = __float2bfloat16_rn(acc / den);
+    }
 }
 
 template <int DH, int GC>
@@ -257,8 +286,8 @@ static int decode_tma_launch(DecodeTmaArgs a, int nt, cudaStream_t s) {
 }
 
 extern "C" int tb_attention_decode_tma_bf16(const void* q, void* out, const void* kc, const void* vc, const int* tok_seq,
-                                            const int* tok_pos, const int* page_table, float* partial, int nt,
-                                            int max_pages, int q_stride, int nh, int nkvh, int dh, int splits,
+                                            const int* tok_pos, const int* page_table, float* partial,
+                                            unsigned* done, int nt, int max_pages, int q_stride, int nh, int nkvh, int dh, int splits,
                                             float scale, cudaStream_t s) {
     if (nh <= 0 || nkvh <= 0 || nh % nkvh || splits < 1) return TB_ERR_ARG;
     if (splits > 1 && !partial) return TB_ERR_ARG;
@@ -268,7 +297,7 @@ extern "C" int tb_attention_decode_tma_bf16(const void* q, void* out, const void
     int rc = 0;
     int* err = tc_error_ptr();
     if (!err) return TB_ERR_UNSUPPORTED;
-    DecodeTmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, tok_seq, tok_pos, page_table, partial, err,
+    DecodeTmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, tok_seq, tok_pos, page_table, partial, done, err,
                     max_pages, q_stride, nh, nkvh, splits, 0, scale * 1.4426950408889634f};
     const int group = nh / nkvh;
     const int gc = group == 1 ? 1 : group == 2 ? 2 : 4;
@@ -279,7 +308,7 @@ extern "C" int tb_attention_decode_tma_bf16(const void* q, void* out, const void
         rc = gc == 1 ? decode_tma_launch<128, 1>(a, nt, s)
                      : gc == 2 ? decode_tma_launch<128, 2>(a, nt, s) : decode_tma_launch<128, 4>(a, nt, s);
     if (rc) return rc;
-    if (splits > 1) {
+    if (splits > 1 && !done) {
         dim3 grid(nt, nh);
         TB_LAUNCH((attention_merge_kernel<__nv_bfloat16>), grid, dh < 128 ? 64 : 128, 0, s, partial,
                   (__nv_bfloat16*)out, nh, dh, splits, tok_pos);

@@ -10,6 +10,9 @@
 //    models/llama/common/src/compute.rs:319-330: every DISTINCT expert is read once per layer, not
 //    once per (token, expert) pair as in the reference's loop); G = 1 without offsets is dense.
 //  * x_rows gathers activation rows (token -> expert dispatch).
+//  * row_group: the rows are NOT sorted; row m belongs to group row_group[m] (a (token, choice) pair and the
+//    expert it chose).  Every block picks its group's rows out of that list by itself, which takes one load
+//    and a ballot, so a decode step needs no dispatch lists at all between the router and the experts.
 //  * DUAL: W[g] is [2N, K]; gate = X.W[g][n], up = X.W[g][N + n]; stores silu(gate) * up
 //    (swiglu, compute.rs:324-326).
 //  * output bfloat16 or float (logits, router).
@@ -42,6 +45,8 @@ struct SkinnyArgs {
     long long w_group_stride;
     int ldx, ldw, ldy;
     int M, N, K, G;
+    const int* row_group;   // [M] group of every row, rows in any order (instead of group_offsets and x_rows), or null
+    int x_div;              // with row_group: row m reads X[m / x_div] and writes Y[m]
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -73,15 +78,35 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
     constexpr int NMAT = DUAL ? 2 : 1;
     __shared__ float red[WN][WK][NMAT][ROWS][SK_COLS + 1];
 
+    __shared__ int list[WK * WN * 32];      // with row_group: the rows of this block's group
+    __shared__ unsigned list_mask[WK * WN];
+
     pdl_sync();
     const int g_idx = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int row_lo = 0, row_hi = a.M;
-    if (a.group_offsets) {
+    const bool listed = a.row_group != nullptr;
+    if (listed) {
+        // M <= threads: thread m looks at row m; rows keep their order inside the group
+        const int m = threadIdx.x;
+        const bool mine = m < a.M && a.row_group[m] == g_idx;
+        const unsigned mask = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) list_mask[warp] = mask;
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < WK * WN; ++w) {
+            const int c = __popc(list_mask[w]);
+            if (w < warp) before += c;
+            total += c;
+        }
+        if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = m;
+        __syncthreads();
+        row_hi = total;
+    } else if (a.group_offsets) {
         row_lo = a.group_offsets[g_idx];
         row_hi = a.group_offsets[g_idx + 1];
     }
     if (row_lo >= row_hi) return;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wk = warp % WK, wn = warp / WK;
     const int n0 = (blockIdx.x * WN + wn) * SK_COLS;
     const int g = lane >> 2, t = lane & 3;
@@ -105,7 +130,8 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
         for (int nt = 0; nt < NT; ++nt) {
             const int m = chunk + nt * 8 + g;
             xp[nt] = nullptr;
-            if (m < row_hi) xp[nt] = a.X + (size_t)(a.x_rows ? a.x_rows[m] : m) * a.ldx + t * 8;
+            if (m < row_hi)
+                xp[nt] = a.X + (size_t)(listed ? list[m] / a.x_div : a.x_rows ? a.x_rows[m] : m) * a.ldx + t * 8;
         }
         float acc[NMAT][NT][4];
 #pragma unroll
@@ -170,7 +196,7 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
                 if (DUAL) v2 += red[w_n][w][NMAT - 1][r][c];
             }
             if (DUAL) v = v / (1.0f + expf(-v)) * v2;
-            stf(static_cast<TY*>(a.Y) + (size_t)(chunk + r) * a.ldy + nb0 + cc, v);
+            stf(static_cast<TY*>(a.Y) + (size_t)(listed ? list[chunk + r] : chunk + r) * a.ldy + nb0 + cc, v);
         }
     }
 }
@@ -209,13 +235,15 @@ extern "C" {
 // since a token picks an expert at most once) and only chooses how many rows a pass takes at once.
 int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
                         long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G, int out_kind,
-                        int max_group_rows, cudaStream_t s) {
+                        int max_group_rows, const int* row_group, int x_div, cudaStream_t s) {
     if (M < 0 || N <= 0 || K <= 0 || G <= 0) return TB_ERR_ARG;
+    if (row_group && (group_offsets || x_rows || x_div < 1)) return TB_ERR_ARG;
+    if (row_group && M > SK_WARPS * 32) return TB_ERR_UNSUPPORTED;
     if (K % 8 || ldx % 8 || ldw % 8 || (w_group_stride % 8)) return TB_ERR_UNSUPPORTED;
     if (((uintptr_t)X | (uintptr_t)W) & 15) return TB_ERR_UNSUPPORTED;
     if (M == 0) return 0;
     SkinnyArgs a{(const __nv_bfloat16*)X, x_rows, (const __nv_bfloat16*)W, Y, group_offsets, w_group_stride,
-                 ldx, ldw, ldy, M, N, K, G};
+                 ldx, ldw, ldy, M, N, K, G, row_group, x_div};
     const int rows = (max_group_rows > 0 && max_group_rows < M) ? max_group_rows : M;
     if (rows <= 8) return skinny_launch_nt<1>(a, out_kind, s);
     if (rows <= 16) return skinny_launch_nt<2>(a, out_kind, s);

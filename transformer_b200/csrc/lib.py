@@ -28,13 +28,13 @@ _SIGNATURES: Dict[str, str] = {
     "tb_rope_cache_f32": "ppppippppiiiii", "tb_rope_cache_bf16": "ppppippppiiiii",
     "tb_attention_f32": "ppppppppppiiiiiiiif", "tb_attention_bf16": "ppppppppppiiiiiiiif",
     "tb_gemm_simt_f32": "pppppliiiiiiii".replace(" ", ""), "tb_gemm_simt_bf16": "pppppliiiiiiii",
-    "tb_gemm_skinny_bf16": "pppppliiiiiiiii",
+    "tb_gemm_skinny_bf16": "pppppliiiiiiiiipi",
     "tb_attention_decode_f32": "ppppppppiiiiiiif", "tb_attention_decode_bf16": "ppppppppiiiiiiif",
     "tb_attention_prefill_bf16": "pppppppppiiiiiif",
     "tb_attention_tc_bf16": "pppppppppiiiiiiiifii",
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
-    "tb_attention_decode_tma_bf16": "ppppppppiiiiiiif",
-    "tb_router_f32": "pppppiiii", "tb_router_bf16": "pppppiiii",
+    "tb_attention_decode_tma_bf16": "pppppppppiiiiiiif",
+    "tb_router_f32": "pppppppppiiii", "tb_router_bf16": "pppppppppiiii",
     "tb_moe_dispatch": "ppppiii", "tb_topk_softmax": "pllppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
     "tb_sample": "plpiififpp",

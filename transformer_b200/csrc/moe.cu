@@ -14,39 +14,9 @@
 //   keep the k largest, ties to the lower expert (the reference sorts descending, compute.rs:381)
 //   w_j = exp(v_j - v_0) / sum_kept exp(v_i - v_0)    softmax over the kept logits (compute.rs:383-392)
 // topk_idx / topk_w are in descending-logit order.
-template <typename T>
-__global__ void __launch_bounds__(ROUTER_WARPS * 32)
-router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restrict__ topk_idx,
-              float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d, int E, int k) {
-    pdl_sync();
-    constexpr int EPL = Vec16<T>::N;
-    extern __shared__ float lg[];   // [E]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int t = blockIdx.x;
-    const T* xr = x1 + (size_t)t * d;
-    const bool vec = (d % EPL) == 0;
-    for (int e = warp; e < E; e += nwarps) {
-        const T* w = wr + (size_t)e * d;
-        float acc = 0.f;
-        if (vec) {
-            for (int c = lane * EPL; c < d; c += 32 * EPL) {
-                float xf[EPL], wf[EPL];
-                Vec16<T>::load(xr + c, xf);
-                Vec16<T>::load(w + c, wf);
-#pragma unroll
-                for (int i = 0; i < EPL; ++i) acc += xf[i] * wf[i];
-            }
-        } else {
-            for (int c = lane; c < d; c += 32) acc += ldf(xr + c) * ldf(w + c);
-        }
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            lg[e] = acc;
-            if (logits_out) logits_out[(size_t)t * E + e] = acc;
-        }
-    }
-    __syncthreads();
-    if (warp != 0) return;
+// The k largest of lg[0..E) and their softmax weights, by one warp; lg is consumed.
+__device__ __forceinline__ void router_pick(float* lg, int* __restrict__ idx_out, float* __restrict__ w_out, int E, int k,
+                                            int lane) {
     float v0 = 0.f, sum = 0.f;
     for (int j = 0; j < k; ++j) {
         float best = -INFINITY;
@@ -72,14 +42,93 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
         const float p = expf(best - v0);
         sum += p;
         if (lane == 0) {
-            topk_idx[(size_t)t * k + j] = bi;
-            topk_w[(size_t)t * k + j] = p;
+            idx_out[j] = bi;
+            w_out[j] = p;
             lg[bi] = __int_as_float(0x7fc00000);   // NaN compares false with everything: taken
         }
         __syncwarp();
     }
     const float inv = 1.0f / sum;
-    for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] *= inv;
+    for (int j = lane; j < k; j += 32) w_out[j] *= inv;
+}
+
+__device__ void dispatch_lists(const int* topk_idx, int* __restrict__ group_offsets, int* __restrict__ sorted_token,
+                               int* __restrict__ pair_row, int M, int k, int E, int* count, int* cursor);
+
+// With `lists` set, the block that finishes last (counted in lists.done, which it leaves at zero again) also
+// builds the dispatch lists from every token's choice: one kernel less between the router and the experts.
+struct DispatchLists {
+    int* group_offsets;
+    int* sorted_token;
+    int* pair_row;
+    unsigned* done;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restrict__ topk_idx,
+              float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d, int E, int k,
+              const DispatchLists lists) {
+    pdl_sync();
+    constexpr int EPL = Vec16<T>::N;
+    extern __shared__ float lg[];   // [E]
+    __shared__ int count[ROUTER_MAX_E + 1];
+    __shared__ int cursor[ROUTER_MAX_E];
+    __shared__ bool last_block;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    const T* xr = x1 + (size_t)t * d;
+    const bool vec = (d % EPL) == 0;
+    for (int e = warp; e < E; e += nwarps) {
+        const T* w = wr + (size_t)e * d;
+        float acc = 0.f;
+        if (vec) {
+            // eight 16-byte loads of each operand are asked for before any is used: the dot product of one
+            // row is short, so what it costs is memory latency, paid once per batch instead of once per load
+            constexpr int UN = 8;
+            for (int c0 = lane * EPL; c0 < d; c0 += 32 * EPL * UN) {
+                uint4 xv[UN], wv[UN];
+#pragma unroll
+                for (int u = 0; u < UN; ++u) {
+                    const int c = c0 + u * 32 * EPL;
+                    xv[u] = wv[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (c < d) {
+                        xv[u] = *reinterpret_cast<const uint4*>(xr + c);
+                        wv[u] = *reinterpret_cast<const uint4*>(w + c);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UN; ++u) {
+                    float xf[EPL], wf[EPL];
+                    Vec16<T>::unpack(xv[u], xf);
+                    Vec16<T>::unpack(wv[u], wf);
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) acc += xf[i] * wf[i];
+                }
+            }
+        } else {
+            for (int c = lane; c < d; c += 32) acc += ldf(xr + c) * ldf(w + c);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            lg[e] = acc;
+            if (logits_out) logits_out[(size_t)t * E + e] = acc;
+        }
+    }
+    __syncthreads();
+    if (warp != 0 && !lists.done) return;
+    if (warp == 0) router_pick(lg, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+    if (!lists.done) return;
+    __threadfence();          // this token's choice is visible before the count says so
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last_block = atomicAdd(lists.done, 1u) == gridDim.x - 1;
+        if (last_block) *lists.done = 0;
+    }
+    __syncthreads();
+    if (!last_block) return;
+    __threadfence();
+    dispatch_lists(topk_idx, lists.group_offsets, lists.sorted_token, lists.pair_row, nt * k, k, E, count, cursor);
 }
 
 // Top-k and weights from router logits that are already in memory: one warp per token.  The logit of
@@ -96,39 +145,7 @@ topk_softmax_kernel(const float* __restrict__ logits, long long ld_t, long long 
     float* lg = lg_all + warp * E;
     for (int e = lane; e < E; e += 32) lg[e] = logits[(size_t)t * ld_t + (size_t)e * ld_e];
     __syncwarp();
-    float v0 = 0.f, sum = 0.f;
-    for (int j = 0; j < k; ++j) {
-        float best = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = lg[e];
-            if (v > best) {
-                best = v;
-                bi = e;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) {
-                best = ov;
-                bi = oi;
-            }
-        }
-        if (bi >= E) bi = 0;
-        if (j == 0) v0 = best;
-        const float p = expf(best - v0);
-        sum += p;
-        if (lane == 0) {
-            topk_idx[(size_t)t * k + j] = bi;
-            topk_w[(size_t)t * k + j] = p;
-            lg[bi] = __int_as_float(0x7fc00000);
-        }
-        __syncwarp();
-    }
-    const float inv = 1.0f / sum;
-    for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] *= inv;
+    router_pick(lg, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
 }
 
 // One block builds the dispatch lists for M = nt * k (token, choice) pairs:
@@ -137,15 +154,11 @@ topk_softmax_kernel(const float* __restrict__ logits, long long ld_t, long long 
 //   pair_row[t * k + j]                      row r that holds the pair's result
 // The order of the rows inside one expert is not fixed; no result depends on it (every row of a
 // product is computed alone, and the combine reads rows through pair_row in the order of j).
-__global__ void __launch_bounds__(1024)
-moe_dispatch_kernel(const int* __restrict__ topk_idx, int* __restrict__ group_offsets,
-                    int* __restrict__ sorted_token, int* __restrict__ pair_row, int M, int k, int E) {
-    pdl_sync();
-    __shared__ int count[ROUTER_MAX_E + 1];
-    __shared__ int cursor[ROUTER_MAX_E];
+__device__ void dispatch_lists(const int* topk_idx, int* __restrict__ group_offsets, int* __restrict__ sorted_token,
+                               int* __restrict__ pair_row, int M, int k, int E, int* count, int* cursor) {
     for (int e = threadIdx.x; e <= E; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < M; p += blockDim.x) atomicAdd(&count[topk_idx[p]], 1);
+    for (int p = threadIdx.x; p < M; p += blockDim.x) atomicAdd(&count[__ldcg(topk_idx + p)], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
@@ -159,10 +172,19 @@ moe_dispatch_kernel(const int* __restrict__ topk_idx, int* __restrict__ group_of
     }
     __syncthreads();
     for (int p = threadIdx.x; p < M; p += blockDim.x) {
-        const int r = atomicAdd(&cursor[topk_idx[p]], 1);
+        const int r = atomicAdd(&cursor[__ldcg(topk_idx + p)], 1);
         sorted_token[r] = p / k;
         pair_row[p] = r;
     }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_dispatch_kernel(const int* __restrict__ topk_idx, int* __restrict__ group_offsets,
+                    int* __restrict__ sorted_token, int* __restrict__ pair_row, int M, int k, int E) {
+    pdl_sync();
+    __shared__ int count[ROUTER_MAX_E + 1];
+    __shared__ int cursor[ROUTER_MAX_E];
+    dispatch_lists(topk_idx, group_offsets, sorted_token, pair_row, M, k, E, count, cursor);
 }
 
 // delta[t, :] = sum_j w[t, j] * y[pair_row[t, j], :]   in float, j ascending = descending logit,
@@ -182,14 +204,14 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
 
 template <typename T>
 static int router_launch(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt,
-                         int d, int E, int k, cudaStream_t s) {
+                         int d, int E, int k, const DispatchLists& lists, cudaStream_t s) {
     if (nt < 0 || d <= 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
     if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
     int warps = E < ROUTER_WARPS ? E : ROUTER_WARPS;
     if (nt >= 1024 && warps > 4) warps = 4;   // many tokens: fewer, longer-lived warps per token
     TB_LAUNCH((router_kernel<T>), nt, warps * 32, (size_t)E * sizeof(float), s, 
-        (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k);
+        (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
     return tb_last_error();
 }
 template <typename T>
@@ -202,13 +224,19 @@ static int combine_launch(const void* y, const int* pair_row, const float* topk_
 }
 
 extern "C" {
-int tb_router_f32(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt, int d,
-                  int E, int k, cudaStream_t s) {
-    return router_launch<float>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k, s);
+// With `done` (one zeroed word that the kernel leaves zeroed) the dispatch lists of tb_moe_dispatch are built
+// by the same kernel; the three list pointers are then required.
+int tb_router_f32(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int* group_offsets,
+                  int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E, int k, cudaStream_t s) {
+    if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
+    return router_launch<float>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k,
+                                DispatchLists{group_offsets, sorted_token, pair_row, done}, s);
 }
-int tb_router_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt, int d,
-                   int E, int k, cudaStream_t s) {
-    return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k, s);
+int tb_router_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int* group_offsets,
+                   int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E, int k, cudaStream_t s) {
+    if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
+    return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k,
+                                        DispatchLists{group_offsets, sorted_token, pair_row, done}, s);
 }
 int tb_topk_softmax(const float* logits, long long ld_t, long long ld_e, int* topk_idx, float* topk_w, int nt, int E, int k,
                     cudaStream_t s) {

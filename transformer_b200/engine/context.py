@@ -40,7 +40,9 @@ class Workspace:
         self.frozen = False     # set while a CUDA graph is being captured
         self.on_grow = on_grow  # called before a buffer is replaced (whoever kept its address must forget it)
 
-    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """``zero``: the buffer is zeroed when it is made (and made anew when it grows); its users leave it
+        zeroed, as the kernels do that count their finished blocks in such a buffer."""
         n = 1
         for s in shape:
             n *= int(s)
@@ -51,7 +53,7 @@ class Workspace:
                 raise RuntimeError(f"scratch buffer {name!r} would grow while a CUDA graph is captured")
             if buf is not None and self.on_grow is not None:
                 self.on_grow()
-            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            buf = (torch.zeros if zero else torch.empty)(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:n].view(*shape)
 
@@ -149,8 +151,8 @@ class StepContext:
         if rec is not None:
             rec(name, self.run_index, tensor.detach().clone())
 
-    def scratch(self, name: str, shape, dtype) -> torch.Tensor:
-        return self.workspace.get(name, shape, dtype)
+    def scratch(self, name: str, shape, dtype, zero: bool = False) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype, zero)
 
     def tiles(self, tq: int) -> AttentionTiles:
         """Each sequence's new tokens cut into tiles of tq tokens (the sizes the model's mixers

@@ -112,11 +112,14 @@ class Attention(Mixer):
         partial = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
-        if USE_DECODE_TMA and self.dtype == torch.bfloat16 and self.dh in (64, 128) and \
-                lib.try_call("tb_attention_decode_tma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
-                             lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
-                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, self.scale):
-            return True
+        if USE_DECODE_TMA and self.dtype == torch.bfloat16 and self.dh in (64, 128):
+            # counters of finished slices: the block that finishes a head's last slice merges them
+            done = ctx.scratch("attn.done", (nt * self.nh,), torch.int32, zero=True) if splits > 1 else None
+            if lib.try_call("tb_attention_decode_tma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                            lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial),
+                            lib.ptr(done), nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits,
+                            self.scale):
+                return True
         return lib.try_call("tb_attention_decode_" + sfx, lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                             lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, self.scale)

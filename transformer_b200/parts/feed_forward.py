@@ -11,7 +11,7 @@ import torch
 
 from ..csrc import lib
 from .base import FEED_FORWARDS, FeedForward, ParamDecl, WeightedRows
-from .linear import gemm_skinny, grouped_matmul, matmul_nt
+from .linear import SKINNY_MAX_PAIRS, gemm_skinny, grouped_matmul, matmul_nt
 
 ROUTER_PRODUCT_ROWS = 256   # above this many tokens the router logits come from the prompt product kernel
 
@@ -62,7 +62,9 @@ class MoE(FeedForward):
             "wd": ParamDecl((self.E, self.d, self.di)),
         }
 
-    def route(self, ctx, x1, logits_out=None):
+    def route(self, ctx, x1, logits_out=None, lists=None):
+        """Experts and weights of every token.  With ``lists`` = (offsets, sorted_token, pair_row) the dispatch lists
+        are wanted too; returns (idx, w, whether the lists were built along the way)."""
         nt = x1.shape[0]
         idx = ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32)
         w = ctx.scratch("moe.topk_w", (nt, self.k), torch.float32)
@@ -73,22 +75,40 @@ class MoE(FeedForward):
             lg = ctx.scratch("moe.logits", (self.E, nt), torch.float32)
             if gemm_skinny(self.weights["router"], x1, lg, out_kind=1):
                 lib.call("tb_topk_softmax", lib.ptr(lg), 1, nt, lib.ptr(idx), lib.ptr(w), nt, self.E, self.k)
-                return idx, w
+                return idx, w, False
+        # a few tokens: the block that finishes last builds the lists, which saves a kernel on the way to the experts
+        fused = lists is not None and nt <= ROUTER_PRODUCT_ROWS
+        done = ctx.scratch("moe.done", (1,), torch.int32, zero=True) if fused else None
+        offsets, sorted_token, pair_row = lists if fused else (None, None, None)
         lib.call("tb_router_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
-                 lib.ptr(idx), lib.ptr(w), lib.ptr(logits_out), nt, self.d, self.E, self.k)
-        return idx, w
+                 lib.ptr(idx), lib.ptr(w), lib.ptr(logits_out), lib.ptr(offsets), lib.ptr(sorted_token),
+                 lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.E, self.k)
+        return idx, w, fused
 
     def forward(self, ctx, x1, out) -> None:
         nt = x1.shape[0]
         M = nt * self.k
         sfx = lib.suffix(self.dtype)
-        idx, w = self.route(ctx, x1)
-        ctx.record("moe.topk_idx", idx)
+        if self.dtype == torch.bfloat16 and M <= SKINNY_MAX_PAIRS and self.d % 8 == 0 and self.di % 8 == 0:
+            # a few tokens: no dispatch lists.  Row p = t * k + j of the experts' products is the pair (token t,
+            # its j-th choice); every block of the product kernel finds its expert's pairs in the router's answer
+            idx, w, _ = self.route(ctx, x1)
+            h = ctx.scratch("moe.h", (M, self.di), self.dtype)
+            y = ctx.scratch("moe.y", (M, self.d), self.dtype)
+            pairs = idx.view(-1)
+            if gemm_skinny(x1, self.weights["wgu"], h, groups=self.E, out_kind=2, max_group_rows=nt, row_group=pairs,
+                           x_div=self.k) and \
+                    gemm_skinny(h, self.weights["wd"], y, groups=self.E, max_group_rows=nt, row_group=pairs):
+                ctx.record("moe.topk_idx", idx)
+                return WeightedRows(y, _identity_rows(M, x1.device), w, self.k)
         offsets = ctx.scratch("moe.offsets", (self.E + 1,), torch.int32)
         sorted_token = ctx.scratch("moe.sorted_token", (M,), torch.int32)
         pair_row = ctx.scratch("moe.pair_row", (M,), torch.int32)
-        lib.call("tb_moe_dispatch", lib.ptr(idx), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
-                 M, self.k, self.E)
+        idx, w, listed = self.route(ctx, x1, lists=(offsets, sorted_token, pair_row))
+        ctx.record("moe.topk_idx", idx)
+        if not listed:
+            lib.call("tb_moe_dispatch", lib.ptr(idx), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
+                     M, self.k, self.E)
         h = ctx.scratch("moe.h", (M, self.di), self.dtype)
         grouped_matmul(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
                        swiglu=True, max_group_rows=nt, scratch=ctx.scratch)
@@ -96,6 +116,17 @@ class MoE(FeedForward):
         grouped_matmul(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E, max_group_rows=nt)
         # the weighted sum over the chosen experts is left to the norm that follows (fused there)
         return WeightedRows(y, pair_row, w, self.k)
+
+
+_IDENTITY_ROWS = {}
+
+
+def _identity_rows(n: int, device) -> torch.Tensor:
+    """0 .. n-1 as int32, made once per size."""
+    key = (n, str(device))
+    if key not in _IDENTITY_ROWS:
+        _IDENTITY_ROWS[key] = torch.arange(n, dtype=torch.int32, device=device)
+    return _IDENTITY_ROWS[key]
 
 
 def sum_weighted_rows(wr: WeightedRows, out) -> None:
