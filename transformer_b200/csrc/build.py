@@ -141,9 +141,21 @@ def ensure_built(verbose: bool = True) -> str:
                 pass
     finally:
         done.set()
+    _prune(os.path.dirname(out_dir), keep=os.path.basename(out_dir))
     if verbose:
         _say(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
     return lib
+
+
+def _prune(parent: str, keep: str) -> None:
+    """Libraries of earlier states of the sources are of no use once the present one is built."""
+    try:
+        for name in os.listdir(parent):
+            old = os.path.join(parent, name)
+            if name != keep and len(name) == len(keep) and os.path.isfile(os.path.join(old, LIB_NAME)):
+                shutil.rmtree(old, ignore_errors=True)
+    except OSError:
+        pass
 
 
 if __name__ == "__main__":

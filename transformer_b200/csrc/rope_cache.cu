@@ -10,19 +10,19 @@
 // Cache of one layer: K and V each [pages, nkvh, TB_PAGE, dh].
 #include "common.cuh"
 
-#define ROPE_HEADS 4   // heads per block
+#define ROPE_HEADS 4   // heads per block when there are few tokens; 32 (a full block of 16-byte items) for prompts
 
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ tok_seq,
                                   const int* __restrict__ tok_pos, const int* __restrict__ page_table,
                                   int max_pages, const float* __restrict__ cos_t,
                                   const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
-                                  int nh, int nkvh, int dh, int half_pairing) {
+                                  int nh, int nkvh, int dh, int half_pairing, int hpb) {
     pdl_sync();
-    // grid: (token, chunk of ROPE_HEADS heads out of q heads, k heads, v heads in that order)
+    // grid: (token, chunk of hpb heads out of q heads, k heads, v heads in that order)
     const int t = blockIdx.x;
-    const int head_lo = blockIdx.y * ROPE_HEADS;
-    const int head_hi = min(head_lo + ROPE_HEADS, nh + 2 * nkvh);
+    const int head_lo = blockIdx.y * hpb;
+    const int head_hi = min(head_lo + hpb, nh + 2 * nkvh);
     const int pos = tok_pos[t];
     const int half = dh >> 1;
     T* row = qkv + (size_t)t * (nh + 2 * nkvh) * dh;
@@ -67,11 +67,11 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict
                                       const int* __restrict__ tok_pos, const int* __restrict__ page_table,
                                       int max_pages, const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
-                                      int nh, int nkvh, int dh, int half_pairing) {
+                                      int nh, int nkvh, int dh, int half_pairing, int hpb) {
     pdl_sync();
     const int t = blockIdx.x;
-    const int head_lo = blockIdx.y * ROPE_HEADS;
-    const int head_hi = min(head_lo + ROPE_HEADS, nh + 2 * nkvh);
+    const int head_lo = blockIdx.y * hpb;
+    const int head_hi = min(head_lo + hpb, nh + 2 * nkvh);
     const int pos = tok_pos[t];
     const int half = dh >> 1;
     T* row = qkv + (size_t)t * (nh + 2 * nkvh) * dh;
@@ -138,14 +138,18 @@ static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, 
     if (nt < 0 || nh <= 0 || nkvh <= 0 || dh <= 0 || (dh & 1)) return TB_ERR_ARG;
     if ((kc == nullptr) != (vc == nullptr)) return TB_ERR_ARG;
     if (nt == 0) return 0;
-    dim3 grid(nt, (nh + 2 * nkvh + ROPE_HEADS - 1) / ROPE_HEADS);
+    // few tokens (decoding): many small blocks, so that every SM has some; prompts: blocks of 256 full threads
+    const int hpb = nt >= 256 ? 8 * ROPE_HEADS : ROPE_HEADS;
+    dim3 grid(nt, (nh + 2 * nkvh + hpb - 1) / hpb);
     if (dh % 16 == 0 && (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc) & 15) == 0) {
-        TB_LAUNCH((rope_cache_vec_kernel<T>), grid, 64, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
-                                                     (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
+        int threads = (hpb * (dh / 16) + 31) / 32 * 32;
+        threads = threads < 64 ? 64 : threads > 256 ? 256 : threads;
+        TB_LAUNCH((rope_cache_vec_kernel<T>), grid, threads, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages,
+                  cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing, hpb);
         return tb_last_error();
     }
-    TB_LAUNCH((rope_cache_kernel<T>), grid, 128, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t,
-                                            (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing);
+    TB_LAUNCH((rope_cache_kernel<T>), grid, nt >= 256 ? 256 : 128, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages,
+              cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing, hpb);
     return tb_last_error();
 }
 
