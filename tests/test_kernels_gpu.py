@@ -357,9 +357,11 @@ def test_sampling_draws_from_the_stated_distribution(V, t, k, p):
 
 
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (300, 688, 4096), (1000, 1376, 136), (77, 40, 688)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (300, 688, 4096), (1000, 1376, 136), (77, 40, 688),
+                                   (1024, 256, 64), (1100, 300, 520), (2500, 1376, 1000), (4096, 688, 136)])
 def test_gemm_tc_dense(M, N, K):
-    """The tcgen05 product against float64, bfloat16 and float outputs, with tails in M, N and K."""
+    """The tcgen05 product against float64, bfloat16 and float outputs, with tails in M, N and K; from 1,024 rows
+    on, two blocks share a tile (cta_group::2)."""
     lib = _lib()
     from transformer_b200.parts.linear import gemm_tc
     a, w = _rand((M, K), torch.bfloat16, 20), _rand((N, K), torch.bfloat16, 21, 0.1)
@@ -371,7 +373,8 @@ def test_gemm_tc_dense(M, N, K):
         assert float((out.double() - ref).abs().max()) <= _tol(out_dtype, float(ref.abs().max()))
 
 
-@pytest.mark.parametrize("E,k,nt,d,di", [(4, 2, 300, 128, 96), (16, 4, 700, 256, 688), (3, 1, 130, 64, 200)])
+@pytest.mark.parametrize("E,k,nt,d,di", [(4, 2, 300, 128, 96), (16, 4, 700, 256, 688), (3, 1, 130, 64, 200),
+                                         (2, 2, 1300, 128, 176), (3, 2, 1700, 64, 80)])      # the last two: pairs of blocks
 def test_gemm_tc_grouped_swiglu_and_down(E, k, nt, d, di):
     """Experts through the prompt path: gather, grouped gate/up with swiglu, grouped down product."""
     lib = _lib()

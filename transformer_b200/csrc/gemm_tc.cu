@@ -1,39 +1,56 @@
 // Matrix products for prompts on the 5th-generation tensor cores (tcgen05), bfloat16 in, float
 // accumulation in tensor memory:   C[m, :] = A[m, :] . B[g(m)]^T
 //
-//   * operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), a
-//     ring of TC_STAGES stages of A [128 x 64] and B [256 x 64];
-//   * one elected thread issues tcgen05.mma (M = 128, N = 256, K = 16 per instruction, cta_group::1);
-//     the accumulator [128 x 256] float lives in TMEM (256 columns);
-//   * tcgen05.commit hands a finished stage back to the TMA warp and, after the last k-block,
-//     the accumulator to the four epilogue warps, which read it with tcgen05.ld, apply the
-//     epilogue in float and store.
-//   Warp roles: 0 = TMA producer, 1 = TMEM allocation + MMA issue, 2..5 = epilogue.
+//   Two forms of one kernel (template parameter CTAS):
+//   * CTAS = 1: a block works on a tile of 128 rows x 256 columns (tcgen05.mma.cta_group::1, M = 128, N = 256);
+//   * CTAS = 2: two blocks (a cluster of two CTAs, cta_group::2) work on one tile of 256 rows x 256 columns:
+//     each holds its own 128 rows of A and HALF of the B tile (128 of the 256 rows of B) in shared memory, and
+//     one tcgen05.mma issued by the leader reads both blocks' operands and writes rows 0..127 of the product
+//     into the leader's tensor memory and rows 128..255 into the other's.  Per block and k-block that is 32 KB
+//     from L2 for 128 x 256 x 64 of product instead of 48 KB, and six ring stages fit instead of four.
+//     Measured: 1.61 against 1.53 PFLOP/s on 8192 x 4096 x 4096 and +7 % on experts with 2,048 rows each; but
+//     with few rows per group the 256-row tiles are mostly padding and there are half as many work items
+//     (decoding at batch 64: -7 %), so the launcher takes pairs only from 1,024 rows per group on;
+//   * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of TC_STAGES stages;
+//     with pairs, both blocks' copies are counted on the LEADER's barrier of the stage;
+//   * tcgen05.commit (with pairs: multicast to both blocks) hands a finished stage back to the TMA warps and, after
+//     the last k-block, the accumulator [128 x 256] float (256 TMEM columns, two of them: the next tile's
+//     products overlap this tile's epilogue) to both blocks' four epilogue warps, which read it with
+//     tcgen05.ld, apply the epilogue in float and store; they hand it back by an arrival on the leader's
+//     barrier.
+//   Warp roles: 0 = TMA producer, 1 = TMEM allocation (+ MMA issue in the leader), 2..5 = epilogue.
 //
 //   * grouped (the experts, models/llama/common/src/compute.rs:319-330 done as one product per
 //     expert over all of its tokens): rows of A are sorted by group; B is the stack of the groups'
-//     matrices viewed as one [G * rows, K] tensor; a block finds its (group, first row) from
+//     matrices viewed as one [G * rows, K] tensor; a pair finds its (group, first row) from
 //     group_offsets.  Rows of the tile that belong to the next group are computed and not stored.
-//   * DUAL (swiglu, compute.rs:324-326): the B tile is 128 gate rows followed by the 128 matching
-//     up rows, so one N = 256 instruction yields both; the epilogue stores silu(gate) * up.
+//   * DUAL (swiglu, compute.rs:324-326): the B tile is 128 gate rows (the leader's half) followed by the
+//     128 matching up rows (the other block's), so one N = 256 instruction yields both; the epilogue stores
+//     silu(gate) * up.
 //   * edges: TMA fills out-of-range rows and the K tail with zeros; stores are predicated.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out sets *error (nonzero), the block
-// stops issuing work, waits (bounded) for its own copies in flight, frees its TMEM and returns.
+// stops issuing work, the leader waits (bounded) for the pair's copies in flight, both blocks meet at the
+// cluster barrier, free their TMEM and return.
 #include <map>
 #include <mutex>
 #include <tuple>
 
 #include "tc_common.cuh"
 
-#define TC_BM 128
+#define TC_BM 128                                  // rows of a tile per block; a pair covers 2 * TC_BM
 #define TC_BN 256
 #define TC_BK 64
-#define TC_STAGES 4
 #define TC_THREADS 192
+#define TC_MAX_STAGES 6
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
-#define TC_B_BYTES (TC_BN * TC_BK * 2)
-#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
+#define TC_BHALF_BYTES (TC_BN / 2 * TC_BK * 2)     // half of the B tile: all that a block of a pair stages
+
+template <int CTAS> struct TcShape {
+    static constexpr int STAGES = CTAS == 2 ? 6 : 4;
+    static constexpr int STAGE_BYTES = TC_A_BYTES + (CTAS == 2 ? 1 : 2) * TC_BHALF_BYTES;
+    static constexpr int ROWS = CTAS * TC_BM;      // rows of a tile
+};
 
 struct TcArgs {
     void* C;
@@ -47,21 +64,20 @@ struct TcArgs {
 };
 
 // ---- the kernel ----------------------------------------------------------------------------
-// Persistent: a block walks the tiles  blockIdx.x, blockIdx.x + gridDim.x, ...  (column tiles of one row
-// tile are neighbours in that order, so concurrent blocks share its A tile in L2).  The TMA ring runs
-// on across tile boundaries, and there are TWO accumulators in TMEM: while the epilogue warps drain
-// tile i, the MMA warp already fills the other one with tile i + 1.
+// Persistent: a block (or pair) walks the tiles  unit, unit + units, ...  (column tiles of one row tile are
+// neighbours in that order, so concurrent units share its A tile in L2).  The TMA ring runs on across tile
+// boundaries.
 struct TcTile {
     int g, row0, row_end, n0;
     bool valid;
 };
 
-__device__ __forceinline__ TcTile tc_tile(const TcArgs& a, int t, int tiles_n, int n_out) {
+__device__ __forceinline__ TcTile tc_tile(const TcArgs& a, int t, int tiles_n, int n_out, int rows) {
     TcTile r;
     const int tm = t / tiles_n;
     r.n0 = (t - tm * tiles_n) * n_out;
     r.g = 0;
-    r.row0 = tm * TC_BM;
+    r.row0 = tm * rows;
     r.row_end = a.M;
     r.valid = r.row0 < a.M;
     if (a.group_offsets) {
@@ -69,10 +85,10 @@ __device__ __forceinline__ TcTile tc_tile(const TcArgs& a, int t, int tiles_n, i
         r.valid = false;
         for (int g = 0; g < a.G; ++g) {
             const int lo = a.group_offsets[g], hi = a.group_offsets[g + 1];
-            const int tiles = (hi - lo + TC_BM - 1) / TC_BM;
+            const int tiles = (hi - lo + rows - 1) / rows;
             if (tm < cum + tiles) {
                 r.g = g;
-                r.row0 = lo + (tm - cum) * TC_BM;
+                r.row0 = lo + (tm - cum) * rows;
                 r.row_end = hi;
                 r.valid = true;
                 break;
@@ -83,15 +99,20 @@ __device__ __forceinline__ TcTile tc_tile(const TcArgs& a, int t, int tiles_n, i
     return r;
 }
 
+template <int CTAS>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                             const __grid_constant__ CUtensorMap map_b,
                                                             const TcArgs a) {
     pdl_sync();
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * TC_STAGES + 4];
+    constexpr int TC_STAGES = TcShape<CTAS>::STAGES, TC_STAGE_BYTES = TcShape<CTAS>::STAGE_BYTES;
+    constexpr bool PAIR = CTAS == 2;
+    __shared__ __align__(8) uint64_t bars[2 * TC_MAX_STAGES + 4];
     __shared__ uint32_t tmem_slot;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0;  // 0 leads the pair
+    const int pair = blockIdx.x / CTAS, pairs = gridDim.x / CTAS;     // this unit of work and how many there are
     const int n_out = a.dual ? TC_BN / 2 : TC_BN;       // output columns of a tile
     const int tiles_n = (a.N + n_out - 1) / n_out;
     const int total = a.tiles_m * tiles_n;
@@ -105,56 +126,67 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(full_bar(s), 1);        // the leader's: its producer arms it with both blocks' bytes
+            mbar_init(empty_bar(s), 1);       // one multicast commit per use
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(acc_full(i), 1);
-            mbar_init(acc_empty(i), 4);       // one arrival per epilogue warp
+            mbar_init(acc_empty(i), 4 * CTAS);    // the leader's: one arrival per epilogue warp of every block
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), 2 * TC_BN);
+    if (warp == 1) {
+        if (PAIR) tmem_alloc_pair(smem_u32(&tmem_slot), 2 * TC_BN);
+        else tmem_alloc(smem_u32(&tmem_slot), 2 * TC_BN);
+    }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();             // both blocks' barriers exist before either signals the other's
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer (both blocks; bytes are counted on the leader's barrier) ----------------
         if (lane == 0) {
             bool ok = true;
             int it = 0;                       // k-blocks handed to the ring so far, over all tiles
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-                const TcTile tl = tc_tile(a, t, tiles_n, n_out);
+            for (int t = pair; t < total && ok; t += pairs) {
+                const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
                 if (!tl.valid) continue;
-                const int b_row = tl.g * a.b_group_rows + tl.n0;
+                const int a_row = tl.row0 + (int)rank * TC_BM;
+                const int b_row = tl.g * a.b_group_rows + tl.n0 + (int)rank * (a.dual ? a.N : TC_BN / 2);
                 for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
                     const int s = it % TC_STAGES;
                     if (it >= TC_STAGES) ok = mbar_wait(empty_bar(s), ((it / TC_STAGES) - 1) & 1, a.error, 1);
                     if (!ok) break;
                     const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-                    mbar_expect_tx(full_bar(s), TC_STAGE_BYTES);
-                    tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, tl.row0);
-                    tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, b_row);
-                    tma_load_2d(sb + TC_B_BYTES / 2, &map_b, full_bar(s), kb * TC_BK,
-                                b_row + (a.dual ? a.N : TC_BN / 2));
+                    if (rank == 0) mbar_expect_tx(full_bar(s), CTAS * TC_STAGE_BYTES);
+                    if (PAIR) {
+                        const uint32_t counted = mapa_shared(full_bar(s), 0);
+                        tma_load_2d_pair(sa, &map_a, counted, kb * TC_BK, a_row);
+                        tma_load_2d_pair(sb, &map_b, counted, kb * TC_BK, b_row);
+                    } else {
+                        tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, a_row);
+                        tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, b_row);
+                        tma_load_2d(sb + TC_BHALF_BYTES, &map_b, full_bar(s), kb * TC_BK,
+                                    b_row + (a.dual ? a.N : TC_BN / 2));
+                    }
                 }
             }
-            if (*(volatile int*)a.error != 0) {
-                // something gave up: let this block's own copies land before the block goes away
+            if (rank == 0 && *(volatile int*)a.error != 0) {
+                // something gave up: let the pair's copies land before the blocks go away
                 for (int i = max(0, it - TC_STAGES); i < it; ++i)
                     mbar_wait(full_bar(i % TC_STAGES), (i / TC_STAGES) & 1, a.error, 4);
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc(TC_BM, TC_BN);
+        // ---------------- MMA issuer: the leader's one thread, for the pair ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc(TcShape<CTAS>::ROWS, TC_BN);
             bool ok = true;
-            int it = 0, lt = 0;               // k-blocks and tiles done by this block
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-                const TcTile tl = tc_tile(a, t, tiles_n, n_out);
+            int it = 0, lt = 0;               // k-blocks and tiles done by this pair
+            for (int t = pair; t < total && ok; t += pairs) {
+                const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
                 if (!tl.valid) continue;
                 const int buf = lt & 1;
                 if (lt >= 2) ok = mbar_wait(acc_empty(buf), ((lt >> 1) - 1) & 1, a.error, 5);   // drained two tiles ago
@@ -170,24 +202,29 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     const uint64_t da = umma_desc(sa), db = umma_desc(sb);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)   // 16 bfloat16 = 32 bytes further along K: +2 in units of 16 bytes
-                        umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-                    umma_commit(empty_bar(s));             // the stage is free once these MMAs have read it
+                        if (PAIR) umma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                        else umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    // the stage is free (in both blocks) once these MMAs have read it
+                    if (PAIR) umma_commit_pair(empty_bar(s), 3);
+                    else umma_commit(empty_bar(s));
                 }
-                umma_commit(acc_full(buf));                // the accumulator is complete (or abandoned)
+                // the accumulator is complete (or abandoned), in both blocks
+                if (PAIR) umma_commit_pair(acc_full(buf), 3);
+                else umma_commit(acc_full(buf));
                 ++lt;
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5, TMEM lanes 32 * (warp % 4) ----------------
+        // ---------------- epilogue: warps 2..5 of both blocks, TMEM lanes 32 * (warp % 4) ----------------
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         bool ok = true;
         int lt = 0;
-        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-            const TcTile tl = tc_tile(a, t, tiles_n, n_out);
+        for (int t = pair; t < total && ok; t += pairs) {
+            const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
             if (!tl.valid) continue;
             const int buf = lt & 1;
-            const int m = tl.row0 + row, n0 = tl.n0;
+            const int m = tl.row0 + (int)rank * TC_BM + row, n0 = tl.n0;
             ok = mbar_wait(acc_full(buf), (lt >> 1) & 1, a.error, 3);
             tc_fence_after();
             if (!ok) break;
@@ -231,16 +268,24 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     }
                 }
             }
-            // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+            // this warp has read its lanes of the accumulator: tell the leader's MMA thread
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(mapa_shared(acc_empty(buf), 0));
+                else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+            }
             ++lt;
         }
     }
+    __syncwarp();
     tc_fence_before();
-    __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 2 * TC_BN);
+    if (PAIR) cluster_sync_all();             // neither block leaves while the other may still signal it
+    else __syncthreads();
+    if (warp == 1) {
+        if (PAIR) tmem_dealloc_pair(tmem_base, 2 * TC_BN);
+        else tmem_dealloc(tmem_base, 2 * TC_BN);
+    }
 }
 
 // Gather rows: out[m, :] = x[rows[m], :]  (activations sorted by expert, so that TMA can fetch tiles)
@@ -305,6 +350,56 @@ int* tc_error_ptr() {
     return p;
 }
 
+template <int CTAS>
+static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, cudaStream_t s) {
+    const size_t smem = (size_t)TcShape<CTAS>::STAGES * TcShape<CTAS>::STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int n_out = a.dual ? TC_BN / 2 : TC_BN, rows = TcShape<CTAS>::ROWS;
+    a.tiles_m = a.group_offsets ? (a.M + rows - 1) / rows + a.G : (a.M + rows - 1) / rows;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = CTAS;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    static int max_units = 0;                  // blocks (or pairs of blocks) that can be resident at once
+    if (!max_units) {
+        int sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        max_units = sms > 0 ? sms : 1;         // one persistent block per SM
+        if (CTAS == 2) {
+            int n = 0;
+            cfg.gridDim = dim3(sms > 1 ? sms / 2 * 2 : 2);
+            cfg.numAttrs = 2;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<CTAS>, &cfg) != cudaSuccess || n <= 0) {
+                cudaGetLastError();
+                max_units = 0;
+                return TB_ERR_UNSUPPORTED;     // no room for a pair of these blocks on this device
+            }
+            max_units = n;
+        }
+    }
+    const int total = a.tiles_m * ((a.N + n_out - 1) / n_out);
+    const int units = total < max_units ? total : max_units;
+    cfg.gridDim = dim3(CTAS * units);
+    cfg.numAttrs = CTAS == 2 ? 2 : 1;
+    tb_state_carveout((const void*)gemm_tc_kernel<CTAS>, TC_THREADS, smem);
+    cudaLaunchKernelEx(&cfg, gemm_tc_kernel<CTAS>, ma, mb, a);
+    return tb_last_error();
+}
+
 extern "C" {
 // C[m] = A[m] . B[g(m)]^T.  A [M, K] (rows sorted by group), B [G, rows_b, K] with rows_b = N (or 2N when
 // out_kind == 2: gate rows then up rows).  out_kind: 0 bfloat16, 1 float, 2 swiglu (bfloat16).
@@ -321,32 +416,16 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
-    rc = make_map(&mb, B, (long long)G * rows_b, K, ldb, TC_BN / 2);
+    rc = make_map(&mb, B, (long long)G * rows_b, K, ldb, TC_BN / 2);     // a box is one block's half of the B tile
     if (rc) return rc;
-    static int* err_ptr = nullptr;
-    static bool configured = false;
-    const size_t smem = (size_t)TC_STAGES * TC_STAGE_BYTES + 1024;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaGetSymbolAddress((void**)&err_ptr, tc_error_word);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    const int n_out = dual ? TC_BN / 2 : TC_BN;
-    const int tiles_m = group_offsets ? (M + TC_BM - 1) / TC_BM + G : (M + TC_BM - 1) / TC_BM;
-    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, tiles_m};
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 1;
-    }
-    const int total = tiles_m * ((N + n_out - 1) / n_out);
-    const int blocks = total < sms ? total : sms;     // one persistent block per SM
-    TB_LAUNCH((gemm_tc_kernel), blocks, TC_THREADS, smem, s, ma, mb, a);
-    return tb_last_error();
+    int* err_ptr = tc_error_ptr();
+    if (!err_ptr) return TB_ERR_UNSUPPORTED;
+    // pairs of blocks pay from about a thousand rows per group on (see the head of this file)
+    const bool pair = (long long)M >= 1024ll * G;
+    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, 0};
+    rc = pair ? tc_launch<2>(ma, mb, a, s) : tc_launch<1>(ma, mb, a, s);
+    if (pair && rc == TB_ERR_UNSUPPORTED) rc = tc_launch<1>(ma, mb, a, s);
+    return rc;
 }
 
 // Nonzero if any tensor-core product gave up on a wait since the last call (1 producer, 2 MMA,
