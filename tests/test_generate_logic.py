@@ -54,14 +54,22 @@ class FakeEngine:
         return [(t[-1] + 1) % self.vocab for t in tokens]
 
 
-def _generate(eng, prompts, max_steps, stop_tokens=(0,)):
+def _generate(eng, prompts, max_steps, stop_tokens=(0,), lookahead=False):
     from transformer_b200.engine import run_batches
+    from transformer_b200.engine.generate import Launched
     limit = [1 << 60 if max_steps is None else max_steps for _ in prompts]
     batches = plan_batches([len(p) for p in prompts], limit, max_batch=eng.table.max_slots,
                            n_pages=eng.table.pages.free, max_context=eng.max_context)
+    how = dict(step_and_sample=eng.step)
+    if lookahead:
+        # a stepper in two halves; "the tokens of the step before, on the device" are the last step's answer
+        def launch(reqs, slots, toks, n_generated, prev):
+            if toks is None:
+                toks = [[prev.payload[prev.reqs.index(r)]] for r in reqs]
+            return Launched(list(reqs), eng.step(reqs, slots, toks, n_generated))
+        how = dict(launch=launch, collect=lambda step: step.payload, lookahead=True)
     out, why, timing = run_batches(batches, prompts, limit, frozenset(stop_tokens), eng.max_context,
-                                   open_slot=eng.table.open, close_slot=eng.table.close,
-                                   length_of=lambda s: eng.table.length[s], step_and_sample=eng.step)
+                                   open_slot=eng.table.open, close_slot=eng.table.close, **how)
     from types import SimpleNamespace
     return SimpleNamespace(tokens=out, finished=why, timing=timing, batches=batches)
 
@@ -80,6 +88,31 @@ def test_loop_batches_stops_and_reuses_slots():
     assert eng.table.slots.free == 3 and eng.table.pages.free == 3, "everything was given back"
     eng.table.check()
     assert res.timing.prefill_tokens == 6 + 3 and res.timing.decode_tokens == (3 + 2 + 2) + (2 + 2 + 2)
+
+
+def test_looking_ahead_gives_the_same_tokens():
+    """The next step is launched before the last one's tokens are seen: same tokens, same reasons, and a
+    sequence that sampled its stop token has been stepped once more (that token is dropped)."""
+    prompts = [[10], [47, 48], [5, 6, 7], [20], [30, 31], [48], [49]]
+    for max_steps in (1, 2, 4, 7):
+        a = _generate(FakeEngine(), prompts, max_steps=max_steps)
+        eng = FakeEngine()
+        b = _generate(eng, prompts, max_steps=max_steps, lookahead=True)
+        assert (a.tokens, a.finished, a.batches) == (b.tokens, b.finished, b.batches), max_steps
+        assert a.timing.prefill_tokens == b.timing.prefill_tokens and a.timing.decode_tokens == b.timing.decode_tokens
+        assert eng.table.slots.free == 3 and eng.table.pages.free == 3
+        eng.table.check()
+    eng = FakeEngine()
+    res = _generate(eng, [[10], [47, 48], [5, 6, 7]], max_steps=4, lookahead=True)
+    assert res.tokens == [[11, 12, 13, 14], [49], [8, 9, 10, 11]]
+    assert eng.steps[1][1] == [[11], [49], [8]]
+    assert eng.steps[2][1] == [[12], [0], [9]], "launched before the stop token was seen"
+    assert eng.steps[3][1] == [[13], [10]], "then the sequence has left"
+    assert len(eng.steps) == 4, "no step is launched for sequences that end by their length"
+    # the context ends a sequence without a step too many: one more would not fit the cache
+    eng = FakeEngine(max_context=8, n_pages=1, max_slots=1)
+    res = _generate(eng, [[1, 2, 3, 4, 5, 6]], max_steps=None, stop_tokens=(), lookahead=True)
+    assert res.tokens == [[7, 8, 9]] and res.finished == ["context"] and len(eng.steps) == 3
 
 
 def test_loop_stops_at_the_context():

@@ -86,47 +86,91 @@ def verdict(token: int, n_generated_before: int, length_before: int, *, stop_tok
     return True, None
 
 
-def run_batches(batches, prompts, limit, stops, max_context, *, open_slot, close_slot, length_of,
-                step_and_sample, clock=time.perf_counter, on_token=None):
+@dataclass
+class Launched:
+    """A step that has been handed to the device: the requests it ran, in order, and whatever the
+    stepper needs to fetch their tokens later."""
+    reqs: List[int]
+    payload: object = None
+
+
+def run_batches(batches, prompts, limit, stops, max_context, *, open_slot, close_slot,
+                step_and_sample=None, launch=None, collect=None, lookahead=False, clock=time.perf_counter,
+                on_token=None):
     """The loop itself, reached only through callables so that it runs without a device:
-    open_slot() -> slot, close_slot(slot), length_of(slot) -> tokens in the cache,
-    step_and_sample(requests, slots, token lists, tokens generated so far per request) -> one new
-    token per request, clock() -> seconds (the real one waits for the device first)."""
+    open_slot() -> slot, close_slot(slot), clock() -> seconds, and the stepper, in one of two forms.
+
+    * ``step_and_sample(requests, slots, token lists, tokens generated so far per request)`` -> one new
+      token per request: every step waits for the one before.
+    * ``launch(requests, slots, token lists or None, generated so far, previous Launched) -> Launched``
+      and ``collect(Launched) -> tokens``.  With ``lookahead`` the next step is launched BEFORE the
+      tokens of the last one are fetched (token lists = None: the stepper feeds the previous step's
+      tokens on the device), so the device never waits for the host.  Whether a sequence ends by its
+      length or by the context is known beforehand; only a stop token is not, so a sequence that samples
+      one has been stepped once more already: that step's token is dropped, and it leaves one step late.
+    """
+    if launch is None:
+        if step_and_sample is None:
+            raise TypeError("run_batches needs step_and_sample, or launch and collect")
+        if lookahead:
+            raise ValueError("looking ahead needs launch and collect")
+
+        def launch(reqs, slots, toks, n_generated, prev):
+            return Launched(list(reqs), step_and_sample(reqs, slots, toks, n_generated))
+
+        def collect(step):
+            return step.payload
     out: List[List[int]] = [[] for _ in prompts]
     why: List[Optional[str]] = [None] * len(prompts)
     timing = Timing()
     for batch in batches:
         slots = {r: open_slot() for r in batch}
         try:
-            live = list(batch)
-            feed = {r: list(prompts[r]) for r in batch}
+            in_cache = {r: len(prompts[r]) for r in batch}      # tokens in the cache after the step being fetched
+            ended = {r: False for r in batch}
+            t0 = clock()
+            step = launch(list(batch), [slots[r] for r in batch], [list(prompts[r]) for r in batch],
+                          [0 for _ in batch], None)
             first = True
-            while live:
-                t0 = clock()
-                ids = step_and_sample(live, [slots[r] for r in live], [feed[r] for r in live],
-                                      [len(out[r]) for r in live])
-                dt = clock() - t0
+            while step is not None:
+                nxt = None
+                if lookahead:
+                    # who goes on unless the token about to be fetched is a stop token
+                    go = [r for r in step.reqs if not ended[r] and
+                          verdict(-1, len(out[r]), in_cache[r], stop_tokens=(), max_new=limit[r],
+                                  max_context=max_context)[1] is None]
+                    if go:
+                        nxt = launch(go, [slots[r] for r in go], None, [len(out[r]) + 1 for r in go], step)
+                ids = collect(step)
+                t1 = clock()
                 if first:
-                    timing.prefill_tokens += sum(len(feed[r]) for r in live)
-                    timing.prefill_seconds += dt
+                    timing.prefill_tokens += sum(len(prompts[r]) for r in step.reqs)
+                    timing.prefill_seconds += t1 - t0
                     first = False
                 else:
-                    timing.decode_tokens += len(live)
-                    timing.decode_seconds += dt
-                nxt = []
-                for r, tok in zip(live, ids):
-                    keep, end = verdict(tok, len(out[r]), length_of(slots[r]), stop_tokens=stops,
-                                        max_new=limit[r], max_context=max_context)
+                    timing.decode_tokens += sum(1 for r in step.reqs if not ended[r])
+                    timing.decode_seconds += t1 - t0
+                t0 = t1
+                go_on, feed = [], []
+                for r, tok in zip(step.reqs, ids):
+                    if ended[r]:
+                        continue                   # stepped once more after its stop token: dropped
+                    keep, end = verdict(tok, len(out[r]), in_cache[r], stop_tokens=stops, max_new=limit[r],
+                                        max_context=max_context)
                     if keep:
                         out[r].append(tok)
                         if on_token is not None:
                             on_token(r, tok)
                     if end is None:
-                        feed[r] = [tok]
-                        nxt.append(r)
+                        go_on.append(r)
+                        feed.append([tok])
                     else:
                         why[r] = end
-                live = nxt
+                        ended[r] = True
+                    in_cache[r] += 1
+                if not lookahead and go_on:
+                    nxt = launch(go_on, [slots[r] for r in go_on], feed, [len(out[r]) for r in go_on], None)
+                step = nxt
         finally:
             for s in slots.values():   # the batch has ended: what it held is used again
                 close_slot(s)
@@ -135,13 +179,15 @@ def run_batches(batches, prompts, limit, stops, max_context, *, open_slot, close
 
 def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[int] = None,
              sample_args: SampleArgs = SampleArgs(), stop_tokens: Optional[Sequence[int]] = None,
-             seed: int = 0, max_batch: Optional[int] = None, on_token: Optional[Callable] = None
-             ) -> GenerationResult:
+             seed: int = 0, max_batch: Optional[int] = None, on_token: Optional[Callable] = None,
+             lookahead: bool = True) -> GenerationResult:
     """Token ids in, token ids out.
 
     max_steps: most tokens generated per request (the reference's MAX_STEPS counts model calls,
     each of which yields one token; default: until the context is full).  stop_tokens default to
-    the ones the model's configuration declares.  ``seed`` fixes the sampler per request."""
+    the ones the model's configuration declares.  ``seed`` fixes the sampler per request.
+    ``lookahead``: launch every step before the tokens of the one before have reached the host (see
+    :func:`run_batches`); the tokens are the same either way."""
     import torch
     from ..sampling.sampler import Sampler
 
@@ -161,17 +207,38 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[in
     if sampler is None:
         sampler = engine._sampler = Sampler(engine.device)
 
-    def step_and_sample(reqs, slots, toks, n_generated):
-        logits = engine.step(slots, toks)
+    pinned = getattr(engine, "_token_landing", None)     # two pinned buffers: at most two steps are in flight
+    if pinned is None:
+        pinned = engine._token_landing = [torch.empty(max(1, table.max_slots), dtype=torch.int32, pin_memory=True)
+                                          for _ in range(2)]
+    turn = [0]
+
+    def launch(reqs, slots, toks, n_generated, prev):
+        if toks is not None:
+            logits = engine.step(slots, toks)
+        else:
+            # the tokens of the step before, straight from the device; picked out if some sequences have left
+            fed = prev.payload[0]
+            if prev.reqs != reqs:
+                at = {r: i for i, r in enumerate(prev.reqs)}
+                fed = fed[torch.tensor([at[r] for r in reqs], dtype=torch.long, device=fed.device)]
+            logits = engine.step(slots, [[0]] * len(reqs), device_tokens=fed)
         u = None if sample_args.greedy else [uniform(seed, r, n) for r, n in zip(reqs, n_generated)]
         ids, _ = sampler.sample(logits, sample_args, u)
-        return ids.cpu().tolist()    # the one device-to-host read of the step (infer.rs:140-146)
+        ids = ids.clone()                        # the sampler's own buffer is overwritten by the next step
+        host = pinned[turn[0] % 2]
+        turn[0] += 1
+        host[:len(reqs)].copy_(ids, non_blocking=True)   # the one device-to-host read of the step (infer.rs:140-146)
+        done = torch.cuda.Event()
+        done.record()
+        return Launched(list(reqs), (ids, host, done))
 
-    def clock():
-        torch.cuda.synchronize(engine.device)
-        return time.perf_counter()
+    def collect(step):
+        _, host, done = step.payload
+        done.synchronize()
+        return host[:len(step.reqs)].tolist()
 
     out, why, timing = run_batches(batches, prompts, limit, stops, spec.max_context, open_slot=engine.open,
-                                   close_slot=engine.close, length_of=engine.cache.length,
-                                   step_and_sample=step_and_sample, clock=clock, on_token=on_token)
+                                   close_slot=engine.close, launch=launch, collect=collect, lookahead=lookahead,
+                                   on_token=on_token)
     return GenerationResult(out, why, timing, batches)
