@@ -472,5 +472,14 @@ def test_attention_decode_tma(nh, nkvh, dh):
             assert got is not None
             assert float((got - c["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"splits {splits}"
             assert int(done.abs().sum()) == 0
+    if (nh, nkvh, dh) == (12, 2, 64):
+        # many more blocks than fit the GPU at once, sequences of very unequal lengths
+        pos = [(37 * i * i + 11 * i) % 900 for i in range(70)]
+        big = attention_case([1] * 70, pos, 16, 8, 64, torch.bfloat16, 1, seed=77)
+        done = torch.zeros(70 * 16, dtype=torch.int32, device="cuda")
+        for splits in (1, 5):
+            got = _run_attention(lib, big, torch.bfloat16, splits, decode=True, tma=True, done=done)
+            assert float((got - big["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"70 sequences, splits {splits}"
+            assert int(done.abs().sum()) == 0 and lib.gemm_tc_status() == 0
     c48 = attention_case([1], [10], 2, 1, 48, torch.bfloat16, 1, seed=1)
     assert _run_attention(lib, c48, torch.bfloat16, 1, decode=True, tma=True) is None, "a head of 48 is refused"
