@@ -374,7 +374,8 @@ def test_gemm_tc_dense(M, N, K):
 
 
 @pytest.mark.parametrize("E,k,nt,d,di", [(4, 2, 300, 128, 96), (16, 4, 700, 256, 688), (3, 1, 130, 64, 200),
-                                         (2, 2, 1300, 128, 176), (3, 2, 1700, 64, 80)])      # the last two: pairs of blocks
+                                         (2, 2, 1300, 128, 176), (3, 2, 1700, 64, 80),       # these two: pairs of blocks
+                                         (16, 4, 64, 256, 688), (5, 2, 20, 64, 440)])        # few rows: narrower tiles
 def test_gemm_tc_grouped_swiglu_and_down(E, k, nt, d, di):
     """Experts through the prompt path: gather, grouped gate/up with swiglu, grouped down product."""
     lib = _lib()

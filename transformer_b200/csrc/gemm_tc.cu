@@ -61,6 +61,7 @@ struct TcArgs {
     int dual;
     int out_float;
     int tiles_m;        // row tiles (with groups: an upper bound; tiles past the last group are skipped)
+    int n_tile;         // rows of B in a tile: a multiple of 16 up to TC_BN (fewer when that fills the SMs better)
 };
 
 // ---- the kernel ----------------------------------------------------------------------------
@@ -113,16 +114,18 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0;  // 0 leads the pair
     const int pair = blockIdx.x / CTAS, pairs = gridDim.x / CTAS;     // this unit of work and how many there are
-    const int n_out = a.dual ? TC_BN / 2 : TC_BN;       // output columns of a tile
+    const int n_out = a.dual ? a.n_tile / 2 : a.n_tile; // output columns of a tile
     const int tiles_n = (a.N + n_out - 1) / n_out;
+    const uint32_t half_bytes = (uint32_t)(a.n_tile / 2) * TC_BK * 2;      // half of the B tile in shared memory
+    const uint32_t stage_tx = TC_A_BYTES + (PAIR ? 1 : 2) * half_bytes;    // bytes one block copies per stage
     const int total = a.tiles_m * tiles_n;
     const int nkb = (a.K + TC_BK - 1) / TC_BK;
 
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (TC_STAGES + s); };
-    auto acc_full = [&](int i) { return bar0 + 8u * (2 * TC_STAGES + i); };
-    auto acc_empty = [&](int i) { return bar0 + 8u * (2 * TC_STAGES + 2 + i); };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (TC_MAX_STAGES + s); };
+    auto acc_full = [&](int i) { return bar0 + 8u * (2 * TC_MAX_STAGES + i); };
+    auto acc_empty = [&](int i) { return bar0 + 8u * (2 * TC_MAX_STAGES + 2 + i); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -150,17 +153,18 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         if (lane == 0) {
             bool ok = true;
             int it = 0;                       // k-blocks handed to the ring so far, over all tiles
+            int s = 0;                        // its stage, and the parity of the stage's last use:
+            uint32_t used = 1;                // kept as counters, since this one thread paces the whole block
             for (int t = pair; t < total && ok; t += pairs) {
                 const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
                 if (!tl.valid) continue;
                 const int a_row = tl.row0 + (int)rank * TC_BM;
-                const int b_row = tl.g * a.b_group_rows + tl.n0 + (int)rank * (a.dual ? a.N : TC_BN / 2);
+                const int b_row = tl.g * a.b_group_rows + tl.n0 + (int)rank * (a.dual ? a.N : a.n_tile / 2);
                 for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
-                    const int s = it % TC_STAGES;
-                    if (it >= TC_STAGES) ok = mbar_wait(empty_bar(s), ((it / TC_STAGES) - 1) & 1, a.error, 1);
+                    if (it >= TC_STAGES) ok = mbar_wait(empty_bar(s), used, a.error, 1);
                     if (!ok) break;
                     const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-                    if (rank == 0) mbar_expect_tx(full_bar(s), CTAS * TC_STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(full_bar(s), CTAS * stage_tx);
                     if (PAIR) {
                         const uint32_t counted = mapa_shared(full_bar(s), 0);
                         tma_load_2d_pair(sa, &map_a, counted, kb * TC_BK, a_row);
@@ -168,8 +172,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     } else {
                         tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, a_row);
                         tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, b_row);
-                        tma_load_2d(sb + TC_BHALF_BYTES, &map_b, full_bar(s), kb * TC_BK,
-                                    b_row + (a.dual ? a.N : TC_BN / 2));
+                        tma_load_2d(sb + half_bytes, &map_b, full_bar(s), kb * TC_BK,
+                                    b_row + (a.dual ? a.N : a.n_tile / 2));
+                    }
+                    if (++s == TC_STAGES) {
+                        s = 0;
+                        used ^= 1;
                     }
                 }
             }
@@ -182,9 +190,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     } else if (warp == 1) {
         // ---------------- MMA issuer: the leader's one thread, for the pair ----------------
         if (lane == 0 && rank == 0) {
-            const uint32_t idesc = umma_idesc(TcShape<CTAS>::ROWS, TC_BN);
+            const uint32_t idesc = umma_idesc(TcShape<CTAS>::ROWS, a.n_tile);
             bool ok = true;
-            int it = 0, lt = 0;               // k-blocks and tiles done by this pair
+            int lt = 0;                       // tiles done by this unit
+            int s = 0;                        // the stage of the next k-block and the parity of its use
+            uint32_t use = 0;
             for (int t = pair; t < total && ok; t += pairs) {
                 const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
                 if (!tl.valid) continue;
@@ -193,9 +203,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + buf * TC_BN;
-                for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
-                    const int s = it % TC_STAGES;
-                    ok = mbar_wait(full_bar(s), (it / TC_STAGES) & 1, a.error, 2);
+                for (int kb = 0; kb < nkb && ok; ++kb) {
+                    ok = mbar_wait(full_bar(s), use, a.error, 2);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
@@ -207,6 +216,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     // the stage is free (in both blocks) once these MMAs have read it
                     if (PAIR) umma_commit_pair(empty_bar(s), 3);
                     else umma_commit(empty_bar(s));
+                    if (++s == TC_STAGES) {
+                        s = 0;
+                        use ^= 1;
+                    }
                 }
                 // the accumulator is complete (or abandoned), in both blocks
                 if (PAIR) umma_commit_pair(acc_full(buf), 3);
@@ -234,19 +247,20 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                 tmem_ld32(trow + c0, v);               // warp-collective: every lane takes part
                 if (a.dual) {
                     float u[32];
-                    tmem_ld32(trow + TC_BN / 2 + c0, u);
+                    tmem_ld32(trow + a.n_tile / 2 + c0, u);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
                 }
-                if (m < tl.row_end && n0 + c0 < a.N) {
+                const int c_end = min(n_out - c0, a.N - n0 - c0);   // columns of this chunk that exist (may be <= 0)
+                if (m < tl.row_end && c_end > 0) {
                     if (a.out_float) {
                         float* dst = static_cast<float*>(a.C) + (size_t)m * a.ldc + n0 + c0;
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (n0 + c0 + i < a.N) dst[i] = v[i];
+                            if (i < c_end) dst[i] = v[i];
                     } else {
                         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.C) + (size_t)m * a.ldc + n0 + c0;
-                        if (n0 + c0 + 32 <= a.N && ((((size_t)m * a.ldc + n0 + c0) & 7) == 0)) {
+                        if (c_end >= 32 && ((((size_t)m * a.ldc + n0 + c0) & 7) == 0)) {
 #pragma unroll
                             for (int i = 0; i < 32; i += 8) {
                                 __nv_bfloat162 p0 = __floats2bfloat162_rn(v[i], v[i + 1]);
@@ -263,7 +277,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                         } else {
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
-                                if (n0 + c0 + i < a.N) dst[i] = __float2bfloat16_rn(v[i]);
+                                if (i < c_end) dst[i] = __float2bfloat16_rn(v[i]);
                         }
                     }
                 }
@@ -359,7 +373,7 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, cud
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int n_out = a.dual ? TC_BN / 2 : TC_BN, rows = TcShape<CTAS>::ROWS;
+    const int n_out = a.dual ? a.n_tile / 2 : a.n_tile, rows = TcShape<CTAS>::ROWS;
     a.tiles_m = a.group_offsets ? (a.M + rows - 1) / rows + a.G : (a.M + rows - 1) / rows;
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(TC_THREADS);
@@ -413,16 +427,39 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     if (M == 0) return 0;
     const int dual = out_kind == 2;
     const int rows_b = dual ? 2 * N : N;
+    // Rows of B per tile.  With about one row tile per group (decoding with many sequences: the product streams
+    // the experts' weights once and has G x column tiles to spread over the SMs) narrower tiles can fill a round
+    // of SMs where the full width leaves a third of them idle; costs in rows loaded per k-block and round.
+    int n_tile = TC_BN;
+    if (group_offsets && (long long)M <= (long long)TC_BM * G) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 1;
+        }
+        long long best = -1;
+        for (int nt = TC_BN; nt >= 64; nt -= 16) {
+            const int out = dual ? nt / 2 : nt;
+            const long long tiles = (long long)G * ((N + out - 1) / out);
+            const long long cost = (tiles + sms - 1) / sms * (64 + nt);
+            if (best < 0 || cost < best) {
+                best = cost;
+                n_tile = nt;
+            }
+        }
+    }
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
-    rc = make_map(&mb, B, (long long)G * rows_b, K, ldb, TC_BN / 2);     // a box is one block's half of the B tile
+    rc = make_map(&mb, B, (long long)G * rows_b, K, ldb, n_tile / 2);     // a box is half of the B tile
     if (rc) return rc;
     int* err_ptr = tc_error_ptr();
     if (!err_ptr) return TB_ERR_UNSUPPORTED;
     // pairs of blocks pay from about a thousand rows per group on (see the head of this file)
     const bool pair = (long long)M >= 1024ll * G;
-    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, 0};
+    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, 0, n_tile};
     rc = pair ? tc_launch<2>(ma, mb, a, s) : tc_launch<1>(ma, mb, a, s);
     if (pair && rc == TB_ERR_UNSUPPORTED) rc = tc_launch<1>(ma, mb, a, s);
     return rc;
