@@ -102,6 +102,33 @@ def test_separate_q_k_v_and_gate_up_are_merged(tmp_path):
     assert e.value.missing == ["blk.0.attn_k.weight"] and not e.value.unexpected
 
 
+def test_one_matrix_per_expert_is_stacked(tmp_path):
+    folder = make_folder(tmp_path, "A")
+    t = load_file(os.path.join(folder, "model.safetensors"))
+    m = LlamaMeta.from_dict(TINY_A)
+    per = dict(t)
+    for i in range(m.nblk):
+        gu = per.pop(f"blk.{i}.ffn_gate_up_exps.weight")
+        dn = per.pop(f"blk.{i}.ffn_down_exps.weight")
+        for e in range(m.nexp):
+            per[f"blk.{i}.ffn_gate.{e}.weight"] = gu[e, :m.di].contiguous()
+            per[f"blk.{i}.ffn_up.{e}.weight"] = gu[e, m.di:].contiguous()
+            per[f"blk.{i}.ffn_down.{e}.weight"] = dn[e].contiguous()
+    d2 = str(tmp_path / "per_expert")
+    os.makedirs(d2)
+    save_file(per, os.path.join(d2, "model.safetensors"))
+    a = load_weights(folder, _rules(TINY_A), torch.bfloat16, CPU)
+    b = load_weights(d2, _rules(TINY_A), torch.bfloat16, CPU)
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    del per["blk.1.ffn_up.2.weight"]
+    d3 = str(tmp_path / "per_expert_bad")
+    os.makedirs(d3)
+    save_file(per, os.path.join(d3, "model.safetensors"))
+    with pytest.raises(WeightError) as e:
+        load_weights(d3, _rules(TINY_A), torch.bfloat16, CPU)
+    assert e.value.missing == ["blk.1.ffn_up.2.weight"] and not e.value.unexpected
+
+
 def test_dense_plan_has_no_router(tmp_path):
     names = {n for r in _rules(TINY_DENSE) for n in r.canonical.names}
     assert "blk.0.ffn_gate_up.weight" in names and not any("gate_inp" in n or "exps" in n for n in names)

@@ -68,9 +68,14 @@ def tensor_plan(m: LlamaMeta) -> List[TensorRule]:
             rules.append(TensorRule(L + ("feed_forward", "wgu"), (E, 2 * di, d), "matrix", (
                 single(p + "ffn_gate_up_exps.weight", (E, 2 * di, d)),
                 Source((p + "ffn_gate_exps.weight", p + "ffn_up_exps.weight"), ((E, di, d), (E, di, d)), "cat1"),
+                # one matrix per expert (files written before the experts were stacked): blk.N.ffn_gate.E.weight, ...
+                Source(tuple(p + f"ffn_{which}.{e}.weight" for e in range(E) for which in ("gate", "up")),
+                       ((di, d),) * (2 * E), "stack0_of_row_pairs"),
             )))
-            rules.append(TensorRule(L + ("feed_forward", "wd"), (E, d, di), "matrix",
-                                    (single(p + "ffn_down_exps.weight", (E, d, di)),)))
+            rules.append(TensorRule(L + ("feed_forward", "wd"), (E, d, di), "matrix", (
+                single(p + "ffn_down_exps.weight", (E, d, di)),
+                Source(tuple(p + f"ffn_down.{e}.weight" for e in range(E)), ((d, di),) * E, "stack0"),
+            )))
         else:
             rules.append(TensorRule(L + ("feed_forward", "wgu"), (2 * di, d), "matrix", (
                 single(p + "ffn_gate_up.weight", (2 * di, d)),

@@ -26,7 +26,9 @@ Dest = Tuple  # e.g. ("layers", 3, "mixer", "wqkv")
 class Source:
     names: Tuple[str, ...]
     shapes: Tuple[Tuple[int, ...], ...]
-    join: str = "single"   # "single" | "cat0" (concatenate along rows) | "cat1" (along dim 1) | "stack0"
+    # "single" | "cat0" (concatenate along rows) | "cat1" (along dim 1) | "stack0" (a new leading dimension) |
+    # "stack0_of_row_pairs" (parts a0, b0, a1, b1, ...: stack of cat0(a_i, b_i): per-expert gate and up matrices)
+    join: str = "single"
 
     def combine(self, parts: Sequence[torch.Tensor]) -> torch.Tensor:
         if self.join == "single":
@@ -37,6 +39,8 @@ class Source:
             return torch.cat(list(parts), dim=1)
         if self.join == "stack0":
             return torch.stack(list(parts), dim=0)
+        if self.join == "stack0_of_row_pairs":
+            return torch.stack([torch.cat([parts[i], parts[i + 1]], dim=0) for i in range(0, len(parts), 2)], dim=0)
         raise ValueError(self.join)
 
 
