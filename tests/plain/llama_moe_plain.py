@@ -115,19 +115,27 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch
     return out
 
 
-def attention_mixer(x1, w_qkv, w_o, positions, sz) -> torch.Tensor:
+def _as_stored(store, x: torch.Tensor) -> torch.Tensor:
+    """``store`` is the rounding an implementation applies where it writes an activation to memory
+    (None: none).  With ``store = lambda x: x.bfloat16().float()`` the functions below predict what a
+    bfloat16 path computes, up to the order of its sums; such a path can be compared with that far more
+    tightly than with the unrounded result.  Sums, softmax, norms and the residual stream stay as they are."""
+    return x if store is None else store(x)
+
+
+def attention_mixer(x1, w_qkv, w_o, positions, sz, store=None) -> torch.Tensor:
     """qkv = x1 Wqkv^T, split into q heads, k heads, v heads in that order, rope(q), rope(k),
     attention, merge heads, times Wo^T (models/llama/common/src/compute.rs:210-270)."""
     nh, nkvh, dh = sz["nh"], sz["nkvh"], sz["dh"]
     n = x1.shape[0]
-    qkv = x1 @ w_qkv.T
+    qkv = _as_stored(store, x1 @ w_qkv.T)
     q = qkv[:, : nh * dh].reshape(n, nh, dh)
     k = qkv[:, nh * dh : (nh + nkvh) * dh].reshape(n, nkvh, dh)
     v = qkv[:, (nh + nkvh) * dh :].reshape(n, nkvh, dh)
-    q = rope(q, positions, sz["theta"], sz["pairing"])
-    k = rope(k, positions, sz["theta"], sz["pairing"])
-    o = causal_attention(q, k, v).reshape(n, nh * dh)
-    return o @ w_o.T
+    q = _as_stored(store, rope(q, positions, sz["theta"], sz["pairing"]))
+    k = _as_stored(store, rope(k, positions, sz["theta"], sz["pairing"]))
+    o = _as_stored(store, causal_attention(q, k, v).reshape(n, nh * dh))
+    return _as_stored(store, o @ w_o.T)
 
 
 def route(logits: torch.Tensor, k: int):
@@ -143,15 +151,16 @@ def silu(z: torch.Tensor) -> torch.Tensor:
     return z / (1.0 + torch.exp(-z))
 
 
-def expert_ffn(x1_tok, w_gate_up, w_down) -> torch.Tensor:
+def expert_ffn(x1_tok, w_gate_up, w_down, store=None) -> torch.Tensor:
     """gate_up = x W_gate_up^T, rows 0..di gate and di..2di up; h = silu(gate) * up; y = h W_down^T
     (models/llama/common/src/compute.rs:320-330)."""
     di = w_down.shape[1]
     gu = w_gate_up @ x1_tok
-    return w_down @ (silu(gu[:di]) * gu[di:])
+    return _as_stored(store, w_down @ _as_stored(store, silu(gu[:di]) * gu[di:]))
 
 
-def moe_feed_forward(x1, w_router, w_gate_up_exps, w_down_exps, k: int, forced=None, margins=None) -> torch.Tensor:
+def moe_feed_forward(x1, w_router, w_gate_up_exps, w_down_exps, k: int, forced=None, margins=None,
+                     store=None) -> torch.Tensor:
     """For every token: router logits, top-k with softmax over the kept logits, the weighted sum of
     the kept experts in descending-logit order (models/llama/common/src/compute.rs:294-333).
 
@@ -173,36 +182,36 @@ def moe_feed_forward(x1, w_router, w_gate_up_exps, w_down_exps, k: int, forced=N
             weights = torch.exp(kept - kept[0])
             weights = weights / weights.sum()
         for e, w in zip(experts, weights):
-            out[a] += w * expert_ffn(x1[a], w_gate_up_exps[e], w_down_exps[e])
+            out[a] += w * expert_ffn(x1[a], w_gate_up_exps[e], w_down_exps[e], store)
     return out
 
 
-def dense_feed_forward(x1, w_gate_up, w_down) -> torch.Tensor:
+def dense_feed_forward(x1, w_gate_up, w_down, store=None) -> torch.Tensor:
     """The feed-forward of a model without experts (models/llama/common/src/compute.rs:278-292)."""
-    return torch.stack([expert_ffn(x1[a], w_gate_up, w_down) for a in range(x1.shape[0])])
+    return torch.stack([expert_ffn(x1[a], w_gate_up, w_down, store) for a in range(x1.shape[0])])
 
 
-def block(x, t: Dict[str, torch.Tensor], i: int, positions, sz, forced=None, margins=None) -> torch.Tensor:
+def block(x, t: Dict[str, torch.Tensor], i: int, positions, sz, forced=None, margins=None, store=None) -> torch.Tensor:
     """x += mixer(norm(x)); x += feed_forward(norm(x)) (models/llama/common/src/compute.rs:204-336)."""
     p = f"blk.{i}."
-    x1 = rms_norm(x, t[p + "attn_norm.weight"], sz["eps"])
-    x = x + attention_mixer(x1, t[p + "attn_qkv.weight"], t[p + "attn_output.weight"], positions, sz)
-    x1 = rms_norm(x, t[p + "ffn_norm.weight"], sz["eps"])
+    x1 = _as_stored(store, rms_norm(x, t[p + "attn_norm.weight"], sz["eps"]))
+    x = x + attention_mixer(x1, t[p + "attn_qkv.weight"], t[p + "attn_output.weight"], positions, sz, store)
+    x1 = _as_stored(store, rms_norm(x, t[p + "ffn_norm.weight"], sz["eps"]))
     if sz["nexp"] > 0:
         x = x + moe_feed_forward(
             x1,
             t[p + "ffn_gate_inp.weight"],
             t[p + "ffn_gate_up_exps.weight"],
             t[p + "ffn_down_exps.weight"],
-            sz["nexp_use"], forced, margins,
+            sz["nexp_use"], forced, margins, store,
         )
     else:
-        x = x + dense_feed_forward(x1, t[p + "ffn_gate_up.weight"], t[p + "ffn_down.weight"])
+        x = x + dense_feed_forward(x1, t[p + "ffn_gate_up.weight"], t[p + "ffn_down.weight"], store)
     return x
 
 
 def forward(cfg: dict, t: Dict[str, torch.Tensor], tokens: Sequence[int],
-            want: Optional[Sequence[int]] = None, forced_routes=None, margins_out=None) -> torch.Tensor:
+            want: Optional[Sequence[int]] = None, forced_routes=None, margins_out=None, store=None) -> torch.Tensor:
     """Logits [len(want), vocab] of one whole sequence that starts at position 0; ``want`` defaults
     to every position.  Final norm and head only on the wanted rows
     (models/llama/common/src/compute.rs:343-365); a missing ``output.weight`` means the head is
@@ -213,11 +222,11 @@ def forward(cfg: dict, t: Dict[str, torch.Tensor], tokens: Sequence[int],
     for i in range(sz["nblk"]):
         # forced_routes[i][a]: experts token a must use in layer i; margins_out[i]: see moe_feed_forward
         m = [] if margins_out is not None else None
-        x = block(x, t, i, positions, sz, None if forced_routes is None else forced_routes[i], m)
+        x = block(x, t, i, positions, sz, None if forced_routes is None else forced_routes[i], m, store)
         if margins_out is not None:
             margins_out.append(m)
     rows = list(range(len(tokens))) if want is None else list(want)
-    x = rms_norm(x[rows], t["output_norm.weight"], sz["eps"])
+    x = _as_stored(store, rms_norm(x[rows], t["output_norm.weight"], sz["eps"]))
     head = t.get("output.weight", t["token_embd.weight"])
     return x @ head.T
 

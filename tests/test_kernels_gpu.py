@@ -443,7 +443,6 @@ def test_attention_prompt_kernel(nh, nkvh, dh):
 def test_attention_tcgen05_kernel(nh, nkvh, dh):
     """The tcgen05 prompt kernel (S and O in tensor memory) on a ragged batch: prompts from zero, shorter and
     longer than its 128-token tile, a continued prompt over 130 cached tokens, a single token."""
-    import os
     lib = _lib()
     dtype = torch.bfloat16
     tq = lib.attention_tc_tile_tokens()
@@ -453,8 +452,7 @@ def test_attention_tcgen05_kernel(nh, nkvh, dh):
     assert lib.try_call("tb_attention_tc_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
                         c["vc"].data_ptr(), c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(), c["tile_nq"].data_ptr(),
                         c["tok_pos"].data_ptr(), c["table"].data_ptr(), c["tiles"], nt, c["max_pages"], nh * dh, nh,
-                        c["nkvh"], dh, c["kc"].shape[0], 1.0 / math.sqrt(dh), int(os.environ.get("TB_V_LBO", "0")),
-                        int(os.environ.get("TB_V_SBO", "0")))
+                        c["nkvh"], dh, c["kc"].shape[0], 1.0 / math.sqrt(dh))
     assert lib.gemm_tc_status() == 0, "a wait inside the kernel gave up"
     got = out.double().cpu().reshape(nt, nh, dh)
     assert float((got - c["ref"]).abs().max()) <= _tol(dtype, 4.0)

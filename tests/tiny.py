@@ -70,7 +70,7 @@ def n_moe_layers(cfg):
     return cfg["num_hidden_layers"] if cfg.get("num_local_experts", 0) else 0
 
 
-def check_request(cfg, tensors, tokens, got_rows, routes, dtype, label=""):
+def check_request(cfg, tensors, tokens, got_rows, routes, dtype, label="", store=None, logit_tol=None):
     """Compare logits of one request with the plain implementation.
 
     got_rows: {position: float logits row}.  routes: None, or int array [moe layers, len(tokens), k]
@@ -82,7 +82,7 @@ def check_request(cfg, tensors, tokens, got_rows, routes, dtype, label=""):
     if routes is not None and len(routes):
         forced = [[[int(e) for e in routes[l][a]] for a in range(len(tokens))] for l in range(len(routes))]
     margins = []
-    ref = P.forward(cfg, tensors, tokens, forced_routes=forced, margins_out=margins)
+    ref = P.forward(cfg, tensors, tokens, forced_routes=forced, margins_out=margins, store=store)
     if forced is not None:
         # the same rule as for the logits below: a number computed on the bfloat16 path may be off
         # by BF16_REL_TOL of the largest magnitude of its row; a gap is the difference of two
@@ -94,6 +94,8 @@ def check_request(cfg, tensors, tokens, got_rows, routes, dtype, label=""):
                         f"{label}: layer {l} token {a}: engine chose {forced[l][a]}, plain {free}, "
                         f"over a clear gap {gap:.3e} (largest router logit {biggest:.3e})")
     tol = FP32_TOL if dtype == "float32" else BF16_REL_TOL * float(ref.abs().max())
+    if logit_tol is not None:
+        tol = logit_tol(float(ref.abs().max()))
     worst = 0.0
     for pos, row in sorted(got_rows.items()):
         diff = float((torch.as_tensor(row) - ref[pos]).abs().max())

@@ -353,11 +353,11 @@ extern "C" {
 int tb_attention_tc_tile_tokens() { return AT_BM; }
 
 // q: [nt, q_stride] (first q head of each token), out: [nt, nh * dh], kc / vc: one layer's cache
-// [cache_pages, nkvh, 64, dh].  v_lbo / v_sbo: 0 = the built-in strides of the V operand's descriptor.
+// [cache_pages, nkvh, 64, dh].
 int tb_attention_tc_bf16(const void* q, void* out, const void* kc, const void* vc, const int* tile_seq,
                          const int* tile_t0, const int* tile_nq, const int* tok_pos, const int* page_table, int tiles,
                          int nt, int max_pages, int q_stride, int nh, int nkvh, int dh, int cache_pages, float scale,
-                         int v_lbo, int v_sbo, cudaStream_t s) {
+                         cudaStream_t s) {
     if (nh <= 0 || nkvh <= 0 || nh % nkvh || tiles < 0 || nt < 0 || cache_pages <= 0) return TB_ERR_ARG;
     if (dh != 64 && dh != 128) return TB_ERR_UNSUPPORTED;
     if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kc | (uintptr_t)vc) & 15)) return TB_ERR_UNSUPPORTED;
@@ -373,7 +373,7 @@ int tb_attention_tc_bf16(const void* q, void* out, const void* kc, const void* v
     int* err_ptr = tc_error_ptr();
     if (!err_ptr) return TB_ERR_UNSUPPORTED;
     AtArgs a{(__nv_bfloat16*)out, tile_seq, tile_t0, tile_nq, tok_pos, page_table, err_ptr, tiles, max_pages, nh, nkvh,
-             scale * 1.4426950408889634f, (unsigned)(v_lbo ? v_lbo : AT_BN * 128), (unsigned)(v_sbo ? v_sbo : 1024)};
+             scale * 1.4426950408889634f, (unsigned)(AT_BN * 128), 1024u};
     return dh == 64 ? attention_tc_launch<64>(mq, mk, mv, a, s) : attention_tc_launch<128>(mq, mk, mv, a, s);
 }
 }

@@ -31,7 +31,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_gemm_skinny_bf16": "pppppliiiiiiiiipi",
     "tb_attention_decode_f32": "ppppppppiiiiiiif", "tb_attention_decode_bf16": "ppppppppiiiiiiif",
     "tb_attention_prefill_bf16": "pppppppppiiiiiif",
-    "tb_attention_tc_bf16": "pppppppppiiiiiiiifii",
+    "tb_attention_tc_bf16": "pppppppppiiiiiiiif",
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
     "tb_attention_decode_tma_bf16": "pppppppppiiiiiiif",
     "tb_router_f32": "pppppppppiiii", "tb_router_bf16": "pppppppppiiii",

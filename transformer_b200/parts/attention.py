@@ -79,7 +79,7 @@ class Attention(Mixer):
             if lib.try_call("tb_attention_tc_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                             lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos),
                             lib.ptr(table), tiles.count, nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh,
-                            self.dh, cache.k.shape[0], self.scale, 0, 0):
+                            self.dh, cache.k.shape[0], self.scale):
                 matmul_nt(o, self.weights["wo"], out)
                 return
         if self.prompt_tile and nt >= 2 * ctx.B:
