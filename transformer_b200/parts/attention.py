@@ -106,13 +106,17 @@ class Attention(Mixer):
         group = self.nh // self.nkvh
         gc = 1 if group == 1 else 2 if group == 2 else 4
         blocks = nt * self.nkvh * ((group + gc - 1) // gc)
-        # enough blocks to fill the GPU eight times over; a function of the batch's shape alone, since a captured
-        # graph keeps it for as long as the sequences grow (a slice that a short sequence leaves empty costs little)
-        splits = int(max(1, min(32, (8 * ctx.engine.sm_count) // blocks)))
+        # Slices of the keys so that the blocks fill the GPU: as many blocks as are resident at once for the kernel
+        # that keeps a ring of pages in shared memory (two per SM: measured best at batch 1 to 16, also with lengths
+        # that differ 16-fold), eight times the SMs for the register-staged one.  A function of the batch's shape
+        # alone, since a captured graph keeps it for as long as the sequences grow (the kernels cut short sequences
+        # into fewer slices by themselves).
+        ring = USE_DECODE_TMA and self.dtype == torch.bfloat16 and self.dh in (64, 128)
+        splits = int(max(1, min(32, ((2 if ring else 8) * ctx.engine.sm_count) // blocks)))
         partial = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
-        if USE_DECODE_TMA and self.dtype == torch.bfloat16 and self.dh in (64, 128):
+        if ring:
             # counters of finished slices: the block that finishes a head's last slice merges them
             done = ctx.scratch("attn.done", (nt * self.nh,), torch.int32, zero=True) if splits > 1 else None
             if lib.try_call("tb_attention_decode_tma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
