@@ -63,7 +63,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 
 // The same, eight values at a time with 16-byte accesses, the row kept in registers between the two
 // passes.  For widths that are a multiple of 8 and at most NORM_THREADS * 8 * NORM_CHUNKS.
-#define NORM_THREADS 256
+#define NORM_THREADS 512
 #define NORM_CHUNKS 4
 template <typename T>
 __global__ void __launch_bounds__(NORM_THREADS)
