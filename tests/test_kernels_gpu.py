@@ -50,7 +50,7 @@ def test_add_rmsnorm(dtype, d):
     y = torch.empty((n, d), dtype=dtype, device="cuda")
     x_in = x.clone()
     lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), delta.data_ptr(), 0, 0, 0, 0, 0, w.data_ptr(), eps,
-             y.data_ptr(), n, d)
+             y.data_ptr(), n, d, w.data_ptr(), 4 * d)          # and some weight to fetch meanwhile: changes nothing
     v = x_in.double() + delta.double()
     assert torch.allclose(x.double(), v, atol=1e-6), "the stream is updated in place with a float sum"
     ref = P.rms_norm(v.cpu(), w.double().cpu(), eps)
@@ -60,7 +60,7 @@ def test_add_rmsnorm(dtype, d):
     y2 = torch.empty((3, d), dtype=dtype, device="cuda")
     before = x.clone()
     lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x.data_ptr(), 0, 0, 0, 0, 0, rows.data_ptr(), w.data_ptr(), eps,
-             y2.data_ptr(), 3, d)
+             y2.data_ptr(), 3, d, 0, 0)
     assert torch.equal(x, before)
     ref2 = P.rms_norm(before[rows.long()].double().cpu(), w.double().cpu(), eps)
     assert float((y2.double().cpu() - ref2).abs().max()) <= _tol(dtype, float(ref2.abs().max()))

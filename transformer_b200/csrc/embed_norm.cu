@@ -23,12 +23,22 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 // which is the combine of the experts' outputs (compute.rs:329-330) fused into the norm that follows.
 // (call sites of rms_norm: models/llama/common/src/compute.rs:207,275,362; the residual sum is the
 //  beta = 1 of the output products, :270,:330.)
+// Bytes that the kernel AFTER this one reads first and that are weights (a router's matrix: 128 KB that one block
+// per token would otherwise wait for from HBM): the last block asks for them to be brought into L2, before it
+// waits for the kernel before it.  Weights do not change, so asking early is always safe.
+__device__ __forceinline__ void warm_l2(const void* warm, int warm_bytes) {
+    if (warm && blockIdx.x == gridDim.x - 1)
+        for (int off = threadIdx.x * 128; off < warm_bytes; off += blockDim.x * 128)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(warm) + off));
+}
+
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                    const T* __restrict__ wy, const int* __restrict__ pair_row,
                                    const float* __restrict__ topk_w, int k,
                                    const int* __restrict__ rows, const float* __restrict__ w,
-                                   float eps, T* __restrict__ y, int d) {
+                                   float eps, T* __restrict__ y, int d, const void* warm, int warm_bytes) {
+    warm_l2(warm, warm_bytes);
     pdl_sync();
     __shared__ float red[33];
     const int i = blockIdx.x;
@@ -70,7 +80,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ wy,
                        const int* __restrict__ pair_row, const float* __restrict__ topk_w, int k,
                        const int* __restrict__ rows, const float* __restrict__ w, float eps, T* __restrict__ y,
-                       int d) {
+                       int d, const void* warm, int warm_bytes) {
+    warm_l2(warm, warm_bytes);
     pdl_sync();
     __shared__ float red[33];
     const int i = blockIdx.x;
@@ -151,18 +162,18 @@ static int embed_launch(const int* tokens, const void* table, float* x, int nt, 
 template <typename T>
 static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const int* pair_row,
                               const float* topk_w, int k, const int* rows, const float* w, float eps,
-                              void* y, int n_out, int d, cudaStream_t s) {
+                              void* y, int n_out, int d, const void* warm, int warm_bytes, cudaStream_t s) {
     if (n_out < 0 || d <= 0) return TB_ERR_ARG;
     if (wy && (delta || !pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
     if (n_out == 0) return 0;
     if (d % 8 == 0 && d <= NORM_THREADS * 8 * NORM_CHUNKS) {
         TB_LAUNCH((add_rmsnorm_vec_kernel<T>), n_out, NORM_THREADS, 0, s, x, (const T*)delta, (const T*)wy, pair_row, topk_w, k,
-                                                                rows, w, eps, (T*)y, d);
+                                                                rows, w, eps, (T*)y, d, warm, warm_bytes);
         return tb_last_error();
     }
     int threads = d >= 2048 ? 512 : 256;
     TB_LAUNCH((add_rmsnorm_kernel<T>), n_out, threads, 0, s, x, (const T*)delta, (const T*)wy, pair_row, topk_w, k, rows, w, eps,
-                                                   (T*)y, d);
+                                                   (T*)y, d, warm, warm_bytes);
     return tb_last_error();
 }
 
@@ -173,12 +184,16 @@ int tb_embed_f32(const int* tokens, const void* table, float* x, int nt, int d, 
 int tb_embed_bf16(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
     return embed_launch<__nv_bfloat16>(tokens, table, x, nt, d, s);
 }
+// warm / warm_bytes: weights that the next kernel reads first, to be asked into L2 meanwhile (or null / 0).
 int tb_add_rmsnorm_f32(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w, int k,
-                       const int* rows, const float* w, float eps, void* y, int n_out, int d, cudaStream_t s) {
-    return add_rmsnorm_launch<float>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, s);
+                       const int* rows, const float* w, float eps, void* y, int n_out, int d, const void* warm,
+                       int warm_bytes, cudaStream_t s) {
+    return add_rmsnorm_launch<float>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, warm, warm_bytes, s);
 }
 int tb_add_rmsnorm_bf16(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w, int k,
-                        const int* rows, const float* w, float eps, void* y, int n_out, int d, cudaStream_t s) {
-    return add_rmsnorm_launch<__nv_bfloat16>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, s);
+                        const int* rows, const float* w, float eps, void* y, int n_out, int d, const void* warm,
+                        int warm_bytes, cudaStream_t s) {
+    return add_rmsnorm_launch<__nv_bfloat16>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, warm,
+                                             warm_bytes, s);
 }
 }

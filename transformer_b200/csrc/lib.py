@@ -24,7 +24,7 @@ _CODES = {"p": _P, "i": _I, "f": _F, "l": _L}
 # name -> argument codes (the trailing stream is added for all but the ones marked no_stream)
 _SIGNATURES: Dict[str, str] = {
     "tb_embed_f32": "pppii", "tb_embed_bf16": "pppii",
-    "tb_add_rmsnorm_f32": "pppppippfpii", "tb_add_rmsnorm_bf16": "pppppippfpii",
+    "tb_add_rmsnorm_f32": "pppppippfpiipi", "tb_add_rmsnorm_bf16": "pppppippfpiipi",
     "tb_rope_cache_f32": "ppppippppiiiii", "tb_rope_cache_bf16": "ppppippppiiiii",
     "tb_attention_f32": "ppppppppppiiiiiiiif", "tb_attention_bf16": "ppppppppppiiiiiiiif",
     "tb_gemm_simt_f32": "pppppliiiiiiii".replace(" ", ""), "tb_gemm_simt_bf16": "pppppliiiiiiii",

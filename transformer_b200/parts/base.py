@@ -73,6 +73,11 @@ class Part:
     def parameters(self) -> Dict[str, ParamDecl]:
         return {}
 
+    def early_weights(self) -> Optional[torch.Tensor]:
+        """A small weight that this part reads first and waits for (a router's matrix), or None.  The part that
+        runs before it may ask for it to be brought into L2 meanwhile (``Norm.forward(..., warm=)``)."""
+        return None
+
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         decl = self.parameters()
         for name, d in decl.items():
@@ -84,6 +89,7 @@ class Part:
 
 class Norm(Part):
     takes_weighted_rows = False
+    can_warm = False           # forward takes ``warm=``: a weight of the next part to fetch into L2 meanwhile
 
     def forward(self, ctx, x, delta, rows, y) -> None:
         raise NotImplementedError

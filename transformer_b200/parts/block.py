@@ -36,11 +36,21 @@ class Layer:
         x1 = ctx.scratch("block.x1", (nt, d), ctx.dtype)
         delta = ctx.scratch("block.delta", (nt, d), ctx.dtype)
         pending = resolve(pending, self.mixer_norm, delta)
-        self.mixer_norm.forward(ctx, x, pending, None, x1)
+        self._norm(self.mixer_norm, self.mixer, ctx, x, pending, x1)
         self.mixer.forward(ctx, x1, delta, cache_view, state)
-        self.feed_forward_norm.forward(ctx, x, delta, None, x1)
+        self._norm(self.feed_forward_norm, self.feed_forward, ctx, x, delta, x1)
         lazy = self.feed_forward.forward(ctx, x1, delta)
         return delta if lazy is None else lazy
+
+
+    @staticmethod
+    def _norm(norm, then, ctx, x, delta, y) -> None:
+        """The norm before the part ``then``; a norm that can do so starts fetching what that part reads first."""
+        early = then.early_weights() if norm.can_warm else None
+        if early is not None:
+            norm.forward(ctx, x, delta, None, y, warm=early)
+        else:
+            norm.forward(ctx, x, delta, None, y)
 
 
 def resolve(pending, norm, into):

@@ -62,6 +62,11 @@ class MoE(FeedForward):
             "wd": ParamDecl((self.E, self.d, self.di)),
         }
 
+    def early_weights(self):
+        """The router's matrix: small, and every token's block waits for all of it."""
+        r = self.weights.get("router")
+        return r if r is not None and r.numel() * r.element_size() <= (1 << 20) else None
+
     def route(self, ctx, x1, logits_out=None, lists=None):
         """Experts and weights of every token.  With ``lists`` = (offsets, sorted_token, pair_row) the dispatch lists
         are wanted too; returns (idx, w, whether the lists were built along the way)."""

@@ -12,6 +12,7 @@ class RMSNorm(Norm):
     """params: width, eps.  Statistics and the residual sum are float; one rounding at the store."""
 
     takes_weighted_rows = True
+    can_warm = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -21,7 +22,7 @@ class RMSNorm(Norm):
     def parameters(self):
         return {"weight": ParamDecl((self.width,), "norm", "ones")}
 
-    def forward(self, ctx, x, delta, rows, y) -> None:
+    def forward(self, ctx, x, delta, rows, y, warm=None) -> None:
         n_out = y.shape[0]
         wy = idx = wts = None
         k = 0
@@ -29,4 +30,4 @@ class RMSNorm(Norm):
             wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
         lib.call("tb_add_rmsnorm_" + lib.suffix(self.dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
                  lib.ptr(wts), k, lib.ptr(rows), lib.ptr(self.weights["weight"]), self.eps, lib.ptr(y), n_out,
-                 self.width)
+                 self.width, lib.ptr(warm), 0 if warm is None else warm.numel() * warm.element_size())
