@@ -82,6 +82,14 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
                        const int* __restrict__ rows, const float* __restrict__ w, float eps, T* __restrict__ y,
                        int d, const void* warm, int warm_bytes) {
     warm_l2(warm, warm_bytes);
+    // this kernel's own weights do not depend on the kernel before it either: they are in registers by the time
+    // the wait is over (they are read once per layer and have left L2 since the last step)
+    float ww[NORM_CHUNKS][8];
+#pragma unroll
+    for (int j = 0; j < NORM_CHUNKS; ++j) {
+        const int c = (threadIdx.x + j * NORM_THREADS) * 8;
+        if (c < d) load8(w + c, ww[j]);
+    }
     pdl_sync();
     __shared__ float red[33];
     const int i = blockIdx.x;
@@ -126,10 +134,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
     for (int j = 0; j < NORM_CHUNKS; ++j) {
         const int c = (threadIdx.x + j * NORM_THREADS) * 8;
         if (c < d) {
-            float ww[8], o[8];
-            load8(w + c, ww);
+            float o[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = v[j][e] * rs * ww[e];
+            for (int e = 0; e < 8; ++e) o[e] = v[j][e] * rs * ww[j][e];
             store8(yr + c, o);
         }
     }

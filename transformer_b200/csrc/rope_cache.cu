@@ -68,7 +68,9 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict
                                       int max_pages, const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc,
                                       int nh, int nkvh, int dh, int half_pairing, int hpb) {
-    pdl_sync();
+    // Positions and the angle table were there before the step began: the angles of this thread's first item are
+    // read before the wait for the kernel that wrote q, k and v (the table is touched once per layer and has
+    // left L2 since the last step).
     const int t = blockIdx.x;
     const int head_lo = blockIdx.y * hpb;
     const int head_hi = min(head_lo + hpb, nh + 2 * nkvh);
@@ -77,11 +79,18 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict
     T* row = qkv + (size_t)t * (nh + 2 * nkvh) * dh;
     const float* cs = cos_t + (size_t)pos * half;
     const float* sn = sin_t + (size_t)pos * half;
+    float c0[8], s0[8];
+    {
+        const int u = threadIdx.x % (dh / 16);
+        load8(cs + u * 8, c0);
+        load8(sn + u * 8, s0);
+    }
     size_t cache_row = 0;
     if (kc) {
         const int page = page_table[(size_t)tok_seq[t] * max_pages + pos / TB_PAGE];
         cache_row = ((size_t)page * nkvh * TB_PAGE + (pos % TB_PAGE)) * dh;
     }
+    pdl_sync();
     const int rot_hi = min(head_hi, nh + nkvh);
     const int units = dh / 16;                 // work items per head: 16 values = 8 pairs each
     for (int idx = threadIdx.x; idx < (rot_hi - head_lo) * units; idx += blockDim.x) {
@@ -89,8 +98,16 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict
         T* h = row + (size_t)head * dh;
         T* dst = head < nh ? h : (kc ? kc + cache_row + (size_t)(head - nh) * TB_PAGE * dh : nullptr);
         float a[8], b[8], c[8], s[8], ya[8], yb[8];
-        load8(cs + u * 8, c);                  // pairs 8u .. 8u+7
-        load8(sn + u * 8, s);
+        if (idx == (int)threadIdx.x) {         // the item whose angles are in registers already
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                c[e] = c0[e];
+                s[e] = s0[e];
+            }
+        } else {
+            load8(cs + u * 8, c);              // pairs 8u .. 8u+7
+            load8(sn + u * 8, s);
+        }
         if (half_pairing) {                    // pair i = (x[i], x[i + half])
             load8(h + u * 8, a);
             load8(h + half + u * 8, b);
