@@ -47,6 +47,7 @@ struct SkinnyArgs {
     int M, N, K, G;
     const int* row_group;   // [M] group of every row, rows in any order (instead of group_offsets and x_rows), or null
     int x_div;              // with row_group: row m reads X[m / x_div] and writes Y[m]
+    int w_constant;         // W is a weight: nothing the kernel before this one may have written
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -81,9 +82,40 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
     __shared__ int list[WK * WN * 32];      // with row_group: the rows of this block's group
     __shared__ unsigned list_mask[WK * WN];
 
-    pdl_sync();
     const int g_idx = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wk = warp % WK, wn = warp / WK;
+    const int n0 = (blockIdx.x * WN + wn) * SK_COLS;
+    const int g = lane >> 2, t = lane & 3;
+
+    const __nv_bfloat16* Wg = a.W + (size_t)g_idx * a.w_group_stride;
+    // weight rows of this thread: columns n0 + g and n0 + g + 8 (clamped; never stored when out of range)
+    const int c0 = min(n0 + g, a.N - 1), c1 = min(n0 + g + 8, a.N - 1);
+    const __nv_bfloat16* w0 = Wg + (size_t)c0 * a.ldw + t * 8;
+    const __nv_bfloat16* w1 = Wg + (size_t)c1 * a.ldw + t * 8;
+    const __nv_bfloat16* u0 = DUAL ? Wg + (size_t)(a.N + c0) * a.ldw + t * 8 : nullptr;
+    const __nv_bfloat16* u1 = DUAL ? Wg + (size_t)(a.N + c1) * a.ldw + t * 8 : nullptr;
+    const int k_steps = (a.K + 31) / 32;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+    // One matrix and no row lists: which weights this block reads does not depend on the kernel before it, so the
+    // first batch of them is in flight before the wait for the activations is over.
+    const bool early = a.w_constant && !a.group_offsets && !a.row_group;
+    uint4 wa[UNR], wb[UNR], ua[DUAL ? UNR : 1], ub[DUAL ? UNR : 1];
+    if (early) {
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int k = (wk + u * WK) * 32;
+            const bool live = k + t * 8 < a.K;
+            wa[u] = live ? ld16w(w0 + k) : zero4;
+            wb[u] = live ? ld16w(w1 + k) : zero4;
+            if (DUAL) {
+                ua[u] = live ? ld16w(u0 + k) : zero4;
+                ub[u] = live ? ld16w(u1 + k) : zero4;
+            }
+        }
+    }
+    pdl_sync();
     int row_lo = 0, row_hi = a.M;
     const bool listed = a.row_group != nullptr;
     if (listed) {
@@ -107,20 +139,6 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
         row_hi = a.group_offsets[g_idx + 1];
     }
     if (row_lo >= row_hi) return;
-    const int wk = warp % WK, wn = warp / WK;
-    const int n0 = (blockIdx.x * WN + wn) * SK_COLS;
-    const int g = lane >> 2, t = lane & 3;
-
-    const __nv_bfloat16* Wg = a.W + (size_t)g_idx * a.w_group_stride;
-    // weight rows of this thread: columns n0 + g and n0 + g + 8 (clamped; never stored when out of range)
-    const int c0 = min(n0 + g, a.N - 1), c1 = min(n0 + g + 8, a.N - 1);
-    const __nv_bfloat16* w0 = Wg + (size_t)c0 * a.ldw + t * 8;
-    const __nv_bfloat16* w1 = Wg + (size_t)c1 * a.ldw + t * 8;
-    const __nv_bfloat16* u0 = DUAL ? Wg + (size_t)(a.N + c0) * a.ldw + t * 8 : nullptr;
-    const __nv_bfloat16* u1 = DUAL ? Wg + (size_t)(a.N + c1) * a.ldw + t * 8 : nullptr;
-    const int k_steps = (a.K + 31) / 32;
-    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-
     for (int chunk = row_lo; chunk < row_hi; chunk += ROWS) {
         const int rows = min(ROWS, row_hi - chunk);
         const int nta = (rows + 7) >> 3;
@@ -142,16 +160,19 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
                 for (int j = 0; j < 4; ++j) acc[i][nt][j] = 0.f;
 
         for (int s0 = wk; s0 < k_steps; s0 += WK * UNR) {
-            uint4 wa[UNR], wb[UNR], ua[DUAL ? UNR : 1], ub[DUAL ? UNR : 1], xv[UNR][NT];
+            uint4 xv[UNR][NT];
+            const bool have = early && s0 == wk && chunk == row_lo;     // the batch read before the wait
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const int k = (s0 + u * WK) * 32;
                 const bool live = k + t * 8 < a.K;      // also false past the last step
-                wa[u] = live ? ld16w(w0 + k) : zero4;
-                wb[u] = live ? ld16w(w1 + k) : zero4;
-                if (DUAL) {
-                    ua[u] = live ? ld16w(u0 + k) : zero4;
-                    ub[u] = live ? ld16w(u1 + k) : zero4;
+                if (!have) {
+                    wa[u] = live ? ld16w(w0 + k) : zero4;
+                    wb[u] = live ? ld16w(w1 + k) : zero4;
+                    if (DUAL) {
+                        ua[u] = live ? ld16w(u0 + k) : zero4;
+                        ub[u] = live ? ld16w(u1 + k) : zero4;
+                    }
                 }
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) xv[u][nt] = (live && nt < nta && xp[nt]) ? ld16(xp[nt] + k) : zero4;
@@ -234,9 +255,11 @@ extern "C" {
 // out_kind: 0 = bfloat16 out, 1 = float out, 2 = swiglu pair (bfloat16 out).  M is the number of rows
 // over all groups; max_group_rows bounds the rows of any ONE group (for experts: the number of tokens,
 // since a token picks an expert at most once) and only chooses how many rows a pass takes at once.
+// w_constant: W holds weights, which no kernel writes, so a block may read its first weights before it waits for
+// the kernel before it; 0 when W is itself a result (the router of prompts passes the activations as W).
 int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
                         long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G, int out_kind,
-                        int max_group_rows, const int* row_group, int x_div, cudaStream_t s) {
+                        int max_group_rows, const int* row_group, int x_div, int w_constant, cudaStream_t s) {
     if (M < 0 || N <= 0 || K <= 0 || G <= 0) return TB_ERR_ARG;
     if (row_group && (group_offsets || x_rows || x_div < 1)) return TB_ERR_ARG;
     if (row_group && M > SK_WARPS * 32) return TB_ERR_UNSUPPORTED;
@@ -244,7 +267,7 @@ int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y
     if (((uintptr_t)X | (uintptr_t)W) & 15) return TB_ERR_UNSUPPORTED;
     if (M == 0) return 0;
     SkinnyArgs a{(const __nv_bfloat16*)X, x_rows, (const __nv_bfloat16*)W, Y, group_offsets, w_group_stride,
-                 ldx, ldw, ldy, M, N, K, G, row_group, x_div};
+                 ldx, ldw, ldy, M, N, K, G, row_group, x_div, w_constant};
     const int rows = (max_group_rows > 0 && max_group_rows < M) ? max_group_rows : M;
     if (rows <= 8) return skinny_launch_nt<1>(a, out_kind, s);
     if (rows <= 16) return skinny_launch_nt<2>(a, out_kind, s);

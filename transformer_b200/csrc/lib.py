@@ -28,7 +28,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_rope_cache_f32": "ppppippppiiiii", "tb_rope_cache_bf16": "ppppippppiiiii",
     "tb_attention_f32": "ppppppppppiiiiiiiif", "tb_attention_bf16": "ppppppppppiiiiiiiif",
     "tb_gemm_simt_f32": "pppppliiiiiiii".replace(" ", ""), "tb_gemm_simt_bf16": "pppppliiiiiiii",
-    "tb_gemm_skinny_bf16": "pppppliiiiiiiiipi",
+    "tb_gemm_skinny_bf16": "pppppliiiiiiiiipii",
     "tb_attention_decode_f32": "ppppppppiiiiiiif", "tb_attention_decode_bf16": "ppppppppiiiiiiif",
     "tb_attention_prefill_bf16": "pppppppppiiiiiif",
     "tb_attention_tc_bf16": "pppppppppiiiiiiiif",

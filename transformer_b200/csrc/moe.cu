@@ -69,8 +69,8 @@ __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restrict__ topk_idx,
               float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d, int E, int k,
               const DispatchLists lists) {
-    pdl_sync();
     constexpr int EPL = Vec16<T>::N;
+    constexpr int UN = 8;
     extern __shared__ float lg[];   // [E]
     __shared__ int count[ROUTER_MAX_E + 1];
     __shared__ int cursor[ROUTER_MAX_E];
@@ -79,22 +79,34 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
     const int t = blockIdx.x;
     const T* xr = x1 + (size_t)t * d;
     const bool vec = (d % EPL) == 0;
+    // The router's weights do not depend on the kernel before this one: the first batch of this warp's first
+    // expert is in registers by the time the wait for the activations is over.
+    uint4 first[UN];
+    if (vec && warp < E) {
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int c = (lane + u * 32) * EPL;
+            first[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (c < d) first[u] = *reinterpret_cast<const uint4*>(wr + (size_t)warp * d + c);
+        }
+    }
+    pdl_sync();
     for (int e = warp; e < E; e += nwarps) {
         const T* w = wr + (size_t)e * d;
         float acc = 0.f;
         if (vec) {
             // eight 16-byte loads of each operand are asked for before any is used: the dot product of one
             // row is short, so what it costs is memory latency, paid once per batch instead of once per load
-            constexpr int UN = 8;
             for (int c0 = lane * EPL; c0 < d; c0 += 32 * EPL * UN) {
                 uint4 xv[UN], wv[UN];
+                const bool have = e == warp && c0 == lane * EPL;     // the batch read before the wait
 #pragma unroll
                 for (int u = 0; u < UN; ++u) {
                     const int c = c0 + u * 32 * EPL;
                     xv[u] = wv[u] = make_uint4(0u, 0u, 0u, 0u);
                     if (c < d) {
                         xv[u] = *reinterpret_cast<const uint4*>(xr + c);
-                        wv[u] = *reinterpret_cast<const uint4*>(w + c);
+                        wv[u] = have ? first[u] : *reinterpret_cast<const uint4*>(w + c);
                     }
                 }
 #pragma unroll

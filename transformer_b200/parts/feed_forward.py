@@ -78,7 +78,7 @@ class MoE(FeedForward):
             # decode product kernel streams x1 once with the roles swapped (experts as its few "tokens"),
             # float accumulation and output [E, nt]; one small kernel then picks the experts
             lg = ctx.scratch("moe.logits", (self.E, nt), torch.float32)
-            if gemm_skinny(self.weights["router"], x1, lg, out_kind=1):
+            if gemm_skinny(self.weights["router"], x1, lg, out_kind=1, w_is_weight=False):
                 lib.call("tb_topk_softmax", lib.ptr(lg), 1, nt, lib.ptr(idx), lib.ptr(w), nt, self.E, self.k)
                 return idx, w, False
         # a few tokens: the block that finishes last builds the lists, which saves a kernel on the way to the experts

@@ -34,10 +34,11 @@ SKINNY_MAX_PAIRS = 128     # grouped: up to this many rows over all groups
 
 
 def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kind=0, max_group_rows=0,
-                row_group=None, x_div=1) -> bool:
+                row_group=None, x_div=1, w_is_weight=True) -> bool:
     """The decode kernel (bfloat16, tensor cores, weights streamed once).  False if it refuses the sizes.
     With ``row_group`` ([M] int32) the rows are unsorted: row m belongs to group row_group[m], reads
-    a[m // x_div] and writes out[m] (no offsets, no gathered rows)."""
+    a[m // x_div] and writes out[m] (no offsets, no gathered rows).  ``w_is_weight=False``: ``w`` was computed by
+    an earlier kernel of the step (the kernel then reads none of it before that kernel has finished)."""
     M, K, N = out.shape[0], a.shape[-1], out.shape[-1]
     if w.dim() == 3:
         stride, ldw = w.stride(0), w.stride(1)
@@ -46,7 +47,7 @@ def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kin
     assert a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
     return lib.try_call("tb_gemm_skinny_bf16", lib.ptr(a), lib.ptr(a_rows), lib.ptr(w), lib.ptr(out),
                         lib.ptr(group_offsets), stride, a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind,
-                        max_group_rows, lib.ptr(row_group), x_div)
+                        max_group_rows, lib.ptr(row_group), x_div, 1 if w_is_weight else 0)
 
 
 def gemm_tc(a, w, out, *, group_offsets=None, groups=1, out_kind=0) -> bool:
