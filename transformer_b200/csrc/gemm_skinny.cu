@@ -98,9 +98,11 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
     const int k_steps = (a.K + 31) / 32;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
-    // One matrix and no row lists: which weights this block reads does not depend on the kernel before it, so the
-    // first batch of them is in flight before the wait for the activations is over.
-    const bool early = a.w_constant && !a.group_offsets && !a.row_group;
+    // Which weights this block reads does not depend on the kernel before it, so the first batch of them is in
+    // flight before the wait for the activations is over.  With groups (experts) the block cannot know yet whether
+    // its group has rows at all: it reads ahead only when most groups do (twice as many rows as groups), so that
+    // what is read for nothing stays a few percent.
+    const bool early = a.w_constant && ((!a.group_offsets && !a.row_group) || a.M >= 2 * a.G);
     uint4 wa[UNR], wb[UNR], ua[DUAL ? UNR : 1], ub[DUAL ? UNR : 1];
     if (early) {
 #pragma unroll
