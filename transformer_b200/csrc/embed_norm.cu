@@ -72,10 +72,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 }
 
 // The same, eight values at a time with 16-byte accesses, the row kept in registers between the two
-// passes.  For widths that are a multiple of 8 and at most NORM_THREADS * 8 * NORM_CHUNKS.
-#define NORM_THREADS 512
+// passes.  For widths that are a multiple of 8 and at most threads * 8 * NORM_CHUNKS.
 #define NORM_CHUNKS 4
-template <typename T>
+// Two forms: for a few rows (decoding) 512 threads per row and the weights read before the dependency wait; for
+// many rows (prompts) 256 lean threads, four blocks to an SM, since there the kernel is bound by memory traffic
+// and the registers of the early read would halve what is resident.
+template <typename T, int NORM_THREADS, bool EARLY>
 __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ wy,
                        const int* __restrict__ pair_row, const float* __restrict__ topk_w, int k,
@@ -84,11 +86,13 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
     warm_l2(warm, warm_bytes);
     // this kernel's own weights do not depend on the kernel before it either: they are in registers by the time
     // the wait is over (they are read once per layer and have left L2 since the last step)
-    float ww[NORM_CHUNKS][8];
+    float ww[EARLY ? NORM_CHUNKS : 1][8];
+    if (EARLY) {
 #pragma unroll
-    for (int j = 0; j < NORM_CHUNKS; ++j) {
-        const int c = (threadIdx.x + j * NORM_THREADS) * 8;
-        if (c < d) load8(w + c, ww[j]);
+        for (int j = 0; j < NORM_CHUNKS; ++j) {
+            const int c = (threadIdx.x + j * NORM_THREADS) * 8;
+            if (c < d) load8(w + c, ww[j]);
+        }
     }
     pdl_sync();
     __shared__ float red[33];
@@ -135,8 +139,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
         const int c = (threadIdx.x + j * NORM_THREADS) * 8;
         if (c < d) {
             float o[8];
+            if (!EARLY) load8(w + c, ww[0]);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = v[j][e] * rs * ww[j][e];
+            for (int e = 0; e < 8; ++e) o[e] = v[j][e] * rs * ww[EARLY ? j : 0][e];
             store8(yr + c, o);
         }
     }
@@ -173,9 +178,14 @@ static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const
     if (n_out < 0 || d <= 0) return TB_ERR_ARG;
     if (wy && (delta || !pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
     if (n_out == 0) return 0;
-    if (d % 8 == 0 && d <= NORM_THREADS * 8 * NORM_CHUNKS) {
-        TB_LAUNCH((add_rmsnorm_vec_kernel<T>), n_out, NORM_THREADS, 0, s, x, (const T*)delta, (const T*)wy, pair_row, topk_w, k,
-                                                                rows, w, eps, (T*)y, d, warm, warm_bytes);
+    if (d % 8 == 0 && n_out <= 256 && d <= 512 * 8 * NORM_CHUNKS) {
+        TB_LAUNCH((add_rmsnorm_vec_kernel<T, 512, true>), n_out, 512, 0, s, x, (const T*)delta, (const T*)wy, pair_row,
+                  topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes);
+        return tb_last_error();
+    }
+    if (d % 8 == 0 && d <= 256 * 8 * NORM_CHUNKS) {
+        TB_LAUNCH((add_rmsnorm_vec_kernel<T, 256, false>), n_out, 256, 0, s, x, (const T*)delta, (const T*)wy, pair_row,
+                  topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes);
         return tb_last_error();
     }
     int threads = d >= 2048 ? 512 : 256;

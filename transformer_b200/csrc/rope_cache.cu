@@ -61,8 +61,10 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int* __restrict__ t
     }
 }
 
-// The same with 8 values per thread and 16-byte accesses (head sizes that are a multiple of 16).
-template <typename T>
+// The same with 8 values per thread and 16-byte accesses (head sizes that are a multiple of 16).  EARLY (a few
+// tokens: decoding) reads the angles before the dependency wait; with many tokens the kernel is bound by memory
+// traffic and does better with the registers that would cost.
+template <typename T, bool EARLY>
 __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict__ tok_seq,
                                       const int* __restrict__ tok_pos, const int* __restrict__ page_table,
                                       int max_pages, const float* __restrict__ cos_t,
@@ -80,7 +82,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict
     const float* cs = cos_t + (size_t)pos * half;
     const float* sn = sin_t + (size_t)pos * half;
     float c0[8], s0[8];
-    {
+    if (EARLY) {
         const int u = threadIdx.x % (dh / 16);
         load8(cs + u * 8, c0);
         load8(sn + u * 8, s0);
@@ -98,7 +100,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const int* __restrict
         T* h = row + (size_t)head * dh;
         T* dst = head < nh ? h : (kc ? kc + cache_row + (size_t)(head - nh) * TB_PAGE * dh : nullptr);
         float a[8], b[8], c[8], s[8], ya[8], yb[8];
-        if (idx == (int)threadIdx.x) {         // the item whose angles are in registers already
+        if (EARLY && idx == (int)threadIdx.x) {   // the item whose angles are in registers already
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 c[e] = c0[e];
@@ -161,8 +163,12 @@ static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, 
     if (dh % 16 == 0 && (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc) & 15) == 0) {
         int threads = (hpb * (dh / 16) + 31) / 32 * 32;
         threads = threads < 64 ? 64 : threads > 256 ? 256 : threads;
-        TB_LAUNCH((rope_cache_vec_kernel<T>), grid, threads, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages,
-                  cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing, hpb);
+        if (nt < 256)
+            TB_LAUNCH((rope_cache_vec_kernel<T, true>), grid, threads, 0, s, (T*)qkv, tok_seq, tok_pos, page_table,
+                      max_pages, cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing, hpb);
+        else
+            TB_LAUNCH((rope_cache_vec_kernel<T, false>), grid, threads, 0, s, (T*)qkv, tok_seq, tok_pos, page_table,
+                      max_pages, cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dh, half_pairing, hpb);
         return tb_last_error();
     }
     TB_LAUNCH((rope_cache_kernel<T>), grid, nt >= 256 ? 256 : 128, 0, s, (T*)qkv, tok_seq, tok_pos, page_table, max_pages,
