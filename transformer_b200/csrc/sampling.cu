@@ -143,9 +143,32 @@ sample_kernel(const float* __restrict__ logits, long long ld, const float* __res
     // argmax with the lowest id among equals
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += blockDim.x) {
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // four 16-byte loads in flight per thread: the row is read once and what it costs is latency
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int n4 = V >> 2;
+        for (int i0 = tid; i0 < n4; i0 += 4 * blockDim.x) {
+            float4 q[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * blockDim.x;
+                q[j] = i < n4 ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {       // ascending ids within the thread: strictly greater keeps the lowest
+                const int i = (i0 + j * blockDim.x) << 2;
+                if (q[j].x > best) { best = q[j].x; bi = i; }
+                if (q[j].y > best) { best = q[j].y; bi = i + 1; }
+                if (q[j].z > best) { best = q[j].z; bi = i + 2; }
+                if (q[j].w > best) { best = q[j].w; bi = i + 3; }
+            }
+        }
+        done = n4 << 2;
+    }
+    for (int i = done + tid; i < V; i += blockDim.x) {
         const float v = row[i];
-        if (v > best) {
+        if (v > best || (v == best && i < bi)) {
             best = v;
             bi = i;
         }
