@@ -67,6 +67,50 @@ def test_add_rmsnorm(dtype, d):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,E,k", [(72, 6, 3), (4096, 16, 4), (136, 33, 1), (8192, 5, 5)])
+def test_add_rmsnorm_that_also_routes(dtype, d, E, k):
+    """The norm that also routes: the same stream and rows as the norm alone, and the experts and weights that the
+    router kernel finds in those rows; what it does not take is refused with nothing done."""
+    lib = _lib()
+    n, eps = 9, 1e-5
+    x = _rand((n, d), torch.float32, 4, 2.0)
+    delta = _rand((n, d), dtype, 5)
+    w = _rand((d,), torch.float32, 6)
+    wr = _rand((E, d), dtype, 7, 0.3)
+    x2 = x.clone()
+    y, y2 = (torch.empty((n, d), dtype=dtype, device="cuda") for _ in range(2))
+    idx, idx2 = (torch.empty((n, k), dtype=torch.int32, device="cuda") for _ in range(2))
+    sc, sc2 = (torch.empty((n, k), dtype=torch.float32, device="cuda") for _ in range(2))
+    took = lib.try_call("tb_add_rmsnorm_router_" + lib.suffix(dtype), x.data_ptr(), delta.data_ptr(), 0, 0, 0, 0, 0,
+                        w.data_ptr(), eps, y.data_ptr(), wr.data_ptr(), idx.data_ptr(), sc.data_ptr(), n, d, E, k)
+    assert took
+    lib.call("tb_add_rmsnorm_" + lib.suffix(dtype), x2.data_ptr(), delta.data_ptr(), 0, 0, 0, 0, 0, w.data_ptr(), eps,
+             y2.data_ptr(), n, d, 0, 0)
+    assert torch.equal(x, x2) and torch.equal(y, y2)
+    lg = torch.empty((n, E), dtype=torch.float32, device="cuda")
+    lib.call("tb_router_" + lib.suffix(dtype), y2.data_ptr(), wr.data_ptr(), idx2.data_ptr(), sc2.data_ptr(),
+             lg.data_ptr(), 0, 0, 0, 0, n, d, E, k)
+    assert torch.equal(idx, idx2), "the same sums in the same order: the same choice"
+    assert float((sc - sc2).abs().max()) < 1e-6
+    rows = torch.tensor([2, 2, 7], dtype=torch.int32, device="cuda")      # gathered rows, as the final norm has them
+    y3 = torch.empty((3, d), dtype=dtype, device="cuda")
+    i3 = torch.empty((3, k), dtype=torch.int32, device="cuda")
+    s3 = torch.empty((3, k), dtype=torch.float32, device="cuda")
+    assert lib.try_call("tb_add_rmsnorm_router_" + lib.suffix(dtype), x.data_ptr(), 0, 0, 0, 0, 0, rows.data_ptr(),
+                        w.data_ptr(), eps, y3.data_ptr(), wr.data_ptr(), i3.data_ptr(), s3.data_ptr(), 3, d, E, k)
+    assert torch.equal(i3, idx[rows.long()]) and torch.equal(y3, y[rows.long()])
+    assert not lib.try_call("tb_add_rmsnorm_router_" + lib.suffix(dtype), x.data_ptr(), delta.data_ptr(), 0, 0, 0, 0, 0,
+                            w.data_ptr(), eps, y.data_ptr(), wr.data_ptr(), idx.data_ptr(), sc.data_ptr(), n, d - 4,
+                            E, k), "a width that is no multiple of 8 is refused"
+    many = torch.zeros((300, d), dtype=torch.float32, device="cuda")
+    assert not lib.try_call("tb_add_rmsnorm_router_" + lib.suffix(dtype), many.data_ptr(), 0, 0, 0, 0, 0, 0, w.data_ptr(),
+                            eps, torch.empty((300, d), dtype=dtype, device="cuda").data_ptr(), wr.data_ptr(),
+                            torch.empty((300, k), dtype=torch.int32, device="cuda").data_ptr(),
+                            torch.empty((300, k), dtype=torch.float32, device="cuda").data_ptr(), 300, d, E, k), \
+        "more rows than it takes: refused (the router's own kernels serve prompts)"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("pairing", ["adjacent", "half"])
 def test_rope_and_cache_write(dtype, pairing):
     lib = _lib()

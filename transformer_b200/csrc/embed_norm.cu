@@ -2,6 +2,7 @@
 //
 // The residual stream is float on both paths, so the residual sum is a 32-bit sum.
 #include "common.cuh"
+#include "router_pick.cuh"
 
 // x[i, :] = table[tokens[i], :]   (models/llama/cuda/src/infer.rs:98-104 copies row by row)
 template <typename T>
@@ -77,12 +78,38 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 // Two forms: for a few rows (decoding) 512 threads per row and the weights read before the dependency wait; for
 // many rows (prompts) 256 lean threads, four blocks to an SM, since there the kernel is bound by memory traffic
 // and the registers of the early read would halve what is resident.
-template <typename T, int NORM_THREADS, bool EARLY>
+// What a feed-forward may ask the norm before it to do in the same kernel (TAIL): the router of the row it has
+// just normalized, i.e. the row's k experts and their weights, by the rules of router_kernel.  The row goes to
+// shared memory as it goes to y (rounded to T), one warp per expert takes its dot product with the router's
+// matrix (whose first part it has read before the dependency wait), one warp picks.  A router kernel of its
+// own would first wait for this kernel to end and then read the row back.
+template <typename T> struct RouterTail {
+    const T* w;        // [E, d], or null: none
+    int E, k;
+    int* idx;          // [rows, k]
+    float* wts;        // [rows, k]
+};
+
+template <typename T, int NORM_THREADS, bool EARLY, bool TAIL>
 __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ wy,
                        const int* __restrict__ pair_row, const float* __restrict__ topk_w, int k,
                        const int* __restrict__ rows, const float* __restrict__ w, float eps, T* __restrict__ y,
-                       int d, const void* warm, int warm_bytes) {
+                       int d, const void* warm, int warm_bytes, const RouterTail<T> tail) {
+    constexpr int EPL = Vec16<T>::N, UN = 8;
+    extern __shared__ __align__(16) unsigned char tail_smem[];      // TAIL: the row as T [d], then logits [E]
+    uint4 first[TAIL ? UN : 1];
+    if (TAIL) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (warp < tail.E) {
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int c = (lane + u * 32) * EPL;
+                first[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (c < d) first[u] = *reinterpret_cast<const uint4*>(tail.w + (size_t)warp * d + c);
+            }
+        }
+    }
     warm_l2(warm, warm_bytes);
     // this kernel's own weights do not depend on the kernel before it either: they are in registers by the time
     // the wait is over (they are read once per layer and have left L2 since the last step)
@@ -143,8 +170,43 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[e] = v[j][e] * rs * ww[EARLY ? j : 0][e];
             store8(yr + c, o);
+            if (TAIL) store8(reinterpret_cast<T*>(tail_smem) + c, o);
         }
     }
+    if (!TAIL) return;
+    __syncthreads();
+    const T* ys = reinterpret_cast<const T*>(tail_smem);
+    float* lg = reinterpret_cast<float*>(tail_smem + (size_t)d * sizeof(T));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e = warp; e < tail.E; e += NORM_THREADS / 32) {
+        const T* we = tail.w + (size_t)e * d;
+        float acc = 0.f;
+        for (int c0 = lane * EPL; c0 < d; c0 += 32 * EPL * UN) {
+            uint4 xv[UN], wv[UN];
+            const bool have = e == warp && c0 == lane * EPL;     // the batch read before the wait
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const int c = c0 + u * 32 * EPL;
+                xv[u] = wv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (c < d) {
+                    xv[u] = *reinterpret_cast<const uint4*>(ys + c);
+                    wv[u] = have ? first[u] : *reinterpret_cast<const uint4*>(we + c);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                float xf[EPL], wf[EPL];
+                Vec16<T>::unpack(xv[u], xf);
+                Vec16<T>::unpack(wv[u], wf);
+#pragma unroll
+                for (int q = 0; q < EPL; ++q) acc += xf[q] * wf[q];
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) lg[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0) router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
 }
 
 template <typename T>
@@ -174,18 +236,30 @@ static int embed_launch(const int* tokens, const void* table, float* x, int nt, 
 template <typename T>
 static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const int* pair_row,
                               const float* topk_w, int k, const int* rows, const float* w, float eps,
-                              void* y, int n_out, int d, const void* warm, int warm_bytes, cudaStream_t s) {
+                              void* y, int n_out, int d, const void* warm, int warm_bytes, cudaStream_t s,
+                              RouterTail<T> tail = RouterTail<T>{nullptr, 0, 0, nullptr, nullptr}) {
     if (n_out < 0 || d <= 0) return TB_ERR_ARG;
     if (wy && (delta || !pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
+    if (tail.w && (tail.E <= 0 || tail.k <= 0 || tail.k > tail.E || !tail.idx || !tail.wts)) return TB_ERR_ARG;
     if (n_out == 0) return 0;
+    if (tail.w) {
+        // the form that also routes: a few rows, a width of 16-byte pieces, the row and the logits in 40 KB
+        const size_t smem = (size_t)d * sizeof(T) + (size_t)tail.E * sizeof(float);
+        if (d % 8 || d > 512 * 8 * NORM_CHUNKS || n_out > 256 || smem > 40 * 1024 ||
+            (reinterpret_cast<uintptr_t>(tail.w) & 15))
+            return TB_ERR_UNSUPPORTED;           // the caller runs the router by itself
+        TB_LAUNCH((add_rmsnorm_vec_kernel<T, 512, true, true>), n_out, 512, smem, s, x, (const T*)delta, (const T*)wy,
+                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, nullptr, 0, tail);
+        return tb_last_error();
+    }
     if (d % 8 == 0 && n_out <= 256 && d <= 512 * 8 * NORM_CHUNKS) {
-        TB_LAUNCH((add_rmsnorm_vec_kernel<T, 512, true>), n_out, 512, 0, s, x, (const T*)delta, (const T*)wy, pair_row,
-                  topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes);
+        TB_LAUNCH((add_rmsnorm_vec_kernel<T, 512, true, false>), n_out, 512, 0, s, x, (const T*)delta, (const T*)wy,
+                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes, tail);
         return tb_last_error();
     }
     if (d % 8 == 0 && d <= 256 * 8 * NORM_CHUNKS) {
-        TB_LAUNCH((add_rmsnorm_vec_kernel<T, 256, false>), n_out, 256, 0, s, x, (const T*)delta, (const T*)wy, pair_row,
-                  topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes);
+        TB_LAUNCH((add_rmsnorm_vec_kernel<T, 256, false, false>), n_out, 256, 0, s, x, (const T*)delta, (const T*)wy,
+                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes, tail);
         return tb_last_error();
     }
     int threads = d >= 2048 ? 512 : 256;
@@ -212,5 +286,23 @@ int tb_add_rmsnorm_bf16(float* x, const void* delta, const void* wy, const int* 
                         int warm_bytes, cudaStream_t s) {
     return add_rmsnorm_launch<__nv_bfloat16>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, warm,
                                              warm_bytes, s);
+}
+// The same, and the router of the rows just normalized in the same kernel (router_w [E, d]; each row's route_k
+// experts and weights into route_idx / route_w [n_out, route_k]).  TB_ERR_UNSUPPORTED for what it does not take
+// (many rows, widths that are no multiple of 8 or do not fit shared memory): nothing has been done then.
+int tb_add_rmsnorm_router_f32(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w,
+                              int k, const int* rows, const float* w, float eps, void* y, const void* router_w,
+                              int* route_idx, float* route_w, int n_out, int d, int E, int route_k, cudaStream_t s) {
+    if (!router_w) return TB_ERR_ARG;
+    return add_rmsnorm_launch<float>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, nullptr, 0, s,
+                                     RouterTail<float>{(const float*)router_w, E, route_k, route_idx, route_w});
+}
+int tb_add_rmsnorm_router_bf16(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w,
+                               int k, const int* rows, const float* w, float eps, void* y, const void* router_w,
+                               int* route_idx, float* route_w, int n_out, int d, int E, int route_k, cudaStream_t s) {
+    if (!router_w) return TB_ERR_ARG;
+    return add_rmsnorm_launch<__nv_bfloat16>(
+        x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, nullptr, 0, s,
+        RouterTail<__nv_bfloat16>{(const __nv_bfloat16*)router_w, E, route_k, route_idx, route_w});
 }
 }

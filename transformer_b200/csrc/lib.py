@@ -25,6 +25,7 @@ _CODES = {"p": _P, "i": _I, "f": _F, "l": _L}
 _SIGNATURES: Dict[str, str] = {
     "tb_embed_f32": "pppii", "tb_embed_bf16": "pppii",
     "tb_add_rmsnorm_f32": "pppppippfpiipi", "tb_add_rmsnorm_bf16": "pppppippfpiipi",
+    "tb_add_rmsnorm_router_f32": "pppppippfppppiiii", "tb_add_rmsnorm_router_bf16": "pppppippfppppiiii",
     "tb_rope_cache_f32": "ppppippppiiiii", "tb_rope_cache_bf16": "ppppippppiiiii",
     "tb_attention_f32": "ppppppppppiiiiiiiif", "tb_attention_bf16": "ppppppppppiiiiiiiif",
     "tb_gemm_simt_f32": "pppppliiiiiiii".replace(" ", ""), "tb_gemm_simt_bf16": "pppppliiiiiiii",

@@ -5,6 +5,7 @@
 // loops over tokens and experts (models/llama/common/src/compute.rs:294-333,375-394).  Here nothing
 // leaves the device: a step has no synchronisation point.
 #include "common.cuh"
+#include "router_pick.cuh"
 
 #define ROUTER_WARPS 16
 #define ROUTER_MAX_E 1024
@@ -14,44 +15,6 @@
 //   keep the k largest, ties to the lower expert (the reference sorts descending, compute.rs:381)
 //   w_j = exp(v_j - v_0) / sum_kept exp(v_i - v_0)    softmax over the kept logits (compute.rs:383-392)
 // topk_idx / topk_w are in descending-logit order.
-// The k largest of lg[0..E) and their softmax weights, by one warp; lg is consumed.
-__device__ __forceinline__ void router_pick(float* lg, int* __restrict__ idx_out, float* __restrict__ w_out, int E, int k,
-                                            int lane) {
-    float v0 = 0.f, sum = 0.f;
-    for (int j = 0; j < k; ++j) {
-        float best = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = lg[e];
-            if (v > best) {   // strictly greater: the lower index stays on ties (e ascends)
-                best = v;
-                bi = e;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) {
-                best = ov;
-                bi = oi;
-            }
-        }
-        if (bi >= E) bi = 0;   // only when every remaining logit is -inf or NaN
-        if (j == 0) v0 = best;
-        const float p = expf(best - v0);
-        sum += p;
-        if (lane == 0) {
-            idx_out[j] = bi;
-            w_out[j] = p;
-            lg[bi] = __int_as_float(0x7fc00000);   // NaN compares false with everything: taken
-        }
-        __syncwarp();
-    }
-    const float inv = 1.0f / sum;
-    for (int j = lane; j < k; j += 32) w_out[j] *= inv;
-}
-
 __device__ void dispatch_lists(const int* topk_idx, int* __restrict__ group_offsets, int* __restrict__ sorted_token,
                                int* __restrict__ pair_row, int M, int k, int E, int* count, int* cursor);
 

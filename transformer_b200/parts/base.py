@@ -87,9 +87,24 @@ class Part:
         self.weights = {n: tensors[n] for n in decl}
 
 
+@dataclass
+class NormTail:
+    """A small computation on the rows a norm has just produced, which the part after the norm asks it to do in
+    the same kernel (the rows are at hand there; a kernel of its own would wait for them and read them back).
+    ``kind`` names it; a norm lists the kinds it can do in ``Norm.tails`` and is handed nothing else.
+    "router": ``weights`` [E, d], ``k``; the norm fills ``index`` [rows, k] (int32) and ``scores`` [rows, k] (float)
+    with each row's k experts and their softmax weights, by the rules of the router kernel."""
+    kind: str
+    weights: Any = None
+    k: int = 0
+    index: Any = None
+    scores: Any = None
+
+
 class Norm(Part):
     takes_weighted_rows = False
     can_warm = False           # forward takes ``warm=``: a weight of the next part to fetch into L2 meanwhile
+    tails: tuple = ()          # kinds of NormTail that forward(..., tail=) computes along the way
 
     def forward(self, ctx, x, delta, rows, y) -> None:
         raise NotImplementedError
@@ -107,6 +122,11 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    def norm_tail(self, ctx, nt: int) -> Optional[NormTail]:
+        """What the norm before this part may compute along the way in a step of ``nt`` rows, or None.  If the norm
+        lists the kind, it is handed the object and ``forward`` receives it back as ``tail=`` (computed)."""
+        return None
+
     def forward(self, ctx, x1, out):
         """Write the contribution into ``out`` and return None, or return a :class:`WeightedRows`
         that stands for it (``out`` is then left alone)."""

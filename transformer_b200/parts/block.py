@@ -38,8 +38,14 @@ class Layer:
         pending = resolve(pending, self.mixer_norm, delta)
         self._norm(self.mixer_norm, self.mixer, ctx, x, pending, x1)
         self.mixer.forward(ctx, x1, delta, cache_view, state)
-        self._norm(self.feed_forward_norm, self.feed_forward, ctx, x, delta, x1)
-        lazy = self.feed_forward.forward(ctx, x1, delta)
+        tail = self.feed_forward.norm_tail(ctx, nt)
+        if tail is not None and tail.kind in self.feed_forward_norm.tails:
+            # the feed-forward's first small step rides along with the norm before it
+            self.feed_forward_norm.forward(ctx, x, delta, None, x1, tail=tail)
+            lazy = self.feed_forward.forward(ctx, x1, delta, tail=tail)
+        else:
+            self._norm(self.feed_forward_norm, self.feed_forward, ctx, x, delta, x1)
+            lazy = self.feed_forward.forward(ctx, x1, delta)
         return delta if lazy is None else lazy
 
 

@@ -10,10 +10,11 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib
-from .base import FEED_FORWARDS, FeedForward, ParamDecl, WeightedRows
+from .base import FEED_FORWARDS, FeedForward, NormTail, ParamDecl, WeightedRows
 from .linear import SKINNY_MAX_PAIRS, gemm_skinny, grouped_matmul, matmul_nt
 
 ROUTER_PRODUCT_ROWS = 256   # above this many tokens the router logits come from the prompt product kernel
+ROUTER_TAIL_ROWS = 256      # up to this many tokens the norm before the experts also routes
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -90,14 +91,22 @@ class MoE(FeedForward):
                  lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.E, self.k)
         return idx, w, fused
 
-    def forward(self, ctx, x1, out) -> None:
+    def norm_tail(self, ctx, nt):
+        """For a few tokens the router rides along with the norm before this part."""
+        if nt > ROUTER_TAIL_ROWS:
+            return None
+        return NormTail("router", weights=self.weights["router"], k=self.k,
+                        index=ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32),
+                        scores=ctx.scratch("moe.topk_w", (nt, self.k), torch.float32))
+
+    def forward(self, ctx, x1, out, tail=None) -> None:
         nt = x1.shape[0]
         M = nt * self.k
         sfx = lib.suffix(self.dtype)
         if self.dtype == torch.bfloat16 and M <= SKINNY_MAX_PAIRS and self.d % 8 == 0 and self.di % 8 == 0:
             # a few tokens: no dispatch lists.  Row p = t * k + j of the experts' products is the pair (token t,
             # its j-th choice); every block of the product kernel finds its expert's pairs in the router's answer
-            idx, w, _ = self.route(ctx, x1)
+            idx, w = (tail.index, tail.scores) if tail is not None else self.route(ctx, x1)[:2]
             h = ctx.scratch("moe.h", (M, self.di), self.dtype)
             y = ctx.scratch("moe.y", (M, self.d), self.dtype)
             pairs = idx.view(-1)
@@ -109,7 +118,10 @@ class MoE(FeedForward):
         offsets = ctx.scratch("moe.offsets", (self.E + 1,), torch.int32)
         sorted_token = ctx.scratch("moe.sorted_token", (M,), torch.int32)
         pair_row = ctx.scratch("moe.pair_row", (M,), torch.int32)
-        idx, w, listed = self.route(ctx, x1, lists=(offsets, sorted_token, pair_row))
+        if tail is not None:
+            idx, w, listed = tail.index, tail.scores, False
+        else:
+            idx, w, listed = self.route(ctx, x1, lists=(offsets, sorted_token, pair_row))
         ctx.record("moe.topk_idx", idx)
         if not listed:
             lib.call("tb_moe_dispatch", lib.ptr(idx), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
