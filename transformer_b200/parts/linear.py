@@ -1,9 +1,13 @@
 """Matrix products  y = x W^T  (weights row-major [out, in], models/llama/common/src/lib.rs:168-180).
 
-float32: always the CUDA-core kernel of this package (plain FFMA: no reduced-precision matrix mode
-can slip in).  bfloat16: dense products go to the library (cuBLAS through ``torch.mm``), as the
-reference hands its ``mat_mul`` to an operator library (compute.rs:425-455); grouped products (the
-experts) and products with float output use this package's kernels.
+float32: always the CUDA-core kernel of this package (plain FFMA: no reduced-precision matrix mode can slip in).
+bfloat16, by the number of rows:
+  * up to 16 rows (decoding): ``gemm_skinny``, which streams the weights once through the tensor cores; the experts
+    of up to 128 (token, expert) pairs too, with the rows unsorted (``row_group``);
+  * more rows, one dense weight: the library (cuBLAS through ``torch.mm``), as the reference hands its ``mat_mul``
+    to an operator library (compute.rs:425-455);
+  * more rows, grouped (the experts of prompts and of wide decode batches) or float output (logits of many rows):
+    ``gemm_tc``, this package's tcgen05 kernel.
 """
 from __future__ import annotations
 
