@@ -64,8 +64,10 @@ def gemm_tc(a, w, out, *, group_offsets=None, groups=1, out_kind=0) -> bool:
                         a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind)
 
 
-def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = a @ w.T for one dense weight; out has a's type, or float (logits)."""
+def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w_is_weight: bool = True) -> None:
+    """out = a @ w.T for one dense weight; out has a's type, or float (logits).  ``w`` is taken to be a weight,
+    which no kernel of the step writes: the decode kernel starts reading it before the kernel that produced ``a``
+    has finished.  Pass ``w_is_weight=False`` if ``w`` is itself a result of the step."""
     M = a.shape[0]
     if M == 0:
         return
@@ -73,7 +75,7 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if a.dtype == torch.float32:
         gemm_simt(a, w, out, out_kind=0)
         return
-    if M <= SKINNY_MAX_ROWS and gemm_skinny(a, w, out, out_kind=1 if to_float else 0):
+    if M <= SKINNY_MAX_ROWS and gemm_skinny(a, w, out, out_kind=1 if to_float else 0, w_is_weight=w_is_weight):
         return
     if (to_float or DENSE_TC) and gemm_tc(a, w, out, out_kind=1 if to_float else 0):
         return
@@ -84,14 +86,14 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def grouped_matmul(a, w, out, *, a_rows=None, group_offsets=None, groups=1, swiglu=False, max_group_rows=0,
-                   scratch=None) -> None:
+                   scratch=None, w_is_weight: bool = True) -> None:
     """out[m] = a[a_rows[m] or m] . w[g(m)]^T over rows sorted by group; with swiglu, w[g] holds gate rows
     then up rows and out = silu(gate) * up.  max_group_rows: a bound on the rows of one group, if known;
     scratch(name, shape, dtype): where the prompt kernel may put the gathered rows."""
     kind = 2 if swiglu else 0
     if a.dtype == torch.bfloat16 and out.shape[0] <= SKINNY_MAX_PAIRS and \
             gemm_skinny(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind,
-                        max_group_rows=max_group_rows):
+                        max_group_rows=max_group_rows, w_is_weight=w_is_weight):
         return
     if a.dtype == torch.bfloat16 and w.is_contiguous():
         src = a
