@@ -326,3 +326,25 @@ def test_a_wide_decode_batch_equals_its_sequences_alone(dtype, folders):
     eng.recorder = None
     eng.cache.table.check()
     assert compared >= 20 and (dtype != "float32" or tipped == 0), (compared, tipped)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_looking_ahead_changes_no_token(dtype, folders):
+    """`generate` launches each step before the last one's tokens have reached the host.  Same tokens and the same
+    reasons to stop as the strict order, greedy and sampled, with stop tokens that really occur (so that sequences
+    leave the batch at different times and a step too many is dropped), over two batches (three slots)."""
+    cfg, _ = CONFIGS["A"]
+    prompts = random_prompts(cfg["vocab_size"], [3, 17, 64, 1, 30, 9, 70], seed=31)
+    engine = tb.load(folders["A"], dtype=dtype, max_tokens=1024, max_slots=3)
+    for args in (tb.SampleArgs(), tb.SampleArgs(temperature=0.9, top_k=20, top_p=0.95)):
+        free = tb.generate(engine, prompts, max_steps=40, stop_tokens=(), sample_args=args, seed=5, lookahead=False)
+        # stop tokens that occur: the most frequent tokens of the free run
+        flat = [t for seq in free.tokens for t in seq]
+        stops = tuple(sorted(set(flat), key=lambda t: -flat.count(t))[:3])
+        strict = tb.generate(engine, prompts, max_steps=40, stop_tokens=stops, sample_args=args, seed=5, lookahead=False)
+        ahead = tb.generate(engine, prompts, max_steps=40, stop_tokens=stops, sample_args=args, seed=5, lookahead=True)
+        assert ahead.tokens == strict.tokens and ahead.finished == strict.finished
+        assert "stop" in strict.finished and any(len(t) < 40 for t in strict.tokens)
+        assert ahead.timing.decode_tokens == strict.timing.decode_tokens
+    engine.cache.table.check()
+    assert engine.cache.table.slots.free == 3
