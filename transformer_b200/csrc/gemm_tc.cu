@@ -17,7 +17,10 @@
 //     the last k-block, the accumulator [128 x 256] float (256 TMEM columns, two of them: the next tile's
 //     products overlap this tile's epilogue) to both blocks' four epilogue warps, which read it with
 //     tcgen05.ld, apply the epilogue in float and store; they hand it back by an arrival on the leader's
-//     barrier.
+//     barrier.  A lane reads one ROW of the accumulator; bfloat16 results therefore pass through a strip of
+//     shared memory per warp and leave as whole 128-byte lines (the product with the short K, the experts'
+//     down projection, was bound by its row-by-row stores: 68.6 -> 60.4 us at 16 x 512 rows, 0.88 -> 1.15
+//     PFLOP/s at 16 x 2,048);
 //   Warp roles: 0 = TMA producer, 1 = TMEM allocation (+ MMA issue in the leader), 2..5 = epilogue.
 //
 //   * grouped (the experts, models/llama/common/src/compute.rs:319-330 done as one product per
@@ -45,6 +48,7 @@
 #define TC_MAX_STAGES 6
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_BHALF_BYTES (TC_BN / 2 * TC_BK * 2)     // half of the B tile: all that a block of a pair stages
+#define TC_STRIP_BYTES (32 * 128)                  // an epilogue warp's strip: 32 rows x 64 bfloat16, on their way out
 
 template <int CTAS> struct TcShape {
     static constexpr int STAGES = CTAS == 2 ? 6 : 4;
@@ -231,6 +235,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         // ---------------- epilogue: warps 2..5 of both blocks, TMEM lanes 32 * (warp % 4) ----------------
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
+        // bfloat16 results whose rows start on 16-byte boundaries leave through this warp's strip of shared memory
+        uint8_t* strip = smem_raw + (smem_base - smem_u32(smem_raw)) + TC_STAGES * TC_STAGE_BYTES + (warp - 2) * TC_STRIP_BYTES;
+        const bool wide = !a.out_float && a.N % 8 == 0 && a.ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(a.C) & 15) == 0;
         bool ok = true;
         int lt = 0;
         for (int t = pair; t < total && ok; t += pairs) {
@@ -251,6 +258,44 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
                 }
+                if (wide) {
+                    // A lane holds 32 columns of ONE row: stored from here, every instruction of the warp would touch
+                    // 32 lines of memory.  So the warp passes two such chunks through its strip of shared memory
+                    // (32 rows x 128 bytes; the 16-byte pieces of a row are XOR-swizzled by the row, so that neither
+                    // side meets a bank twice) and stores whole 128-byte lines, four rows an instruction.
+                    const int half = (c0 >> 5) & 1;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                        __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                        uint4 pk;
+                        pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                        pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                        pk.z = *reinterpret_cast<uint32_t*>(&p2);
+                        pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                        *reinterpret_cast<uint4*>(strip + lane * 128 + (((half * 4 + j) ^ (lane & 7)) << 4)) = pk;
+                    }
+                    if (half == 1 || c0 + 32 >= n_out) {
+                        __syncwarp();
+                        const int cb = c0 - half * 32;                       // the strip's first column in the tile
+                        const int cols = min(n_out - cb, a.N - n0 - cb);     // its columns that exist (may be <= 0)
+                        const int p = lane & 7;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = (lane >> 3) + 4 * i;
+                            const int mr = m - lane + r;
+                            if (mr < tl.row_end && 8 * p + 8 <= cols) {       // N is a multiple of 8 here: no torn piece
+                                const uint4 pk = *reinterpret_cast<const uint4*>(strip + r * 128 + ((p ^ (r & 7)) << 4));
+                                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.C) + (size_t)mr * a.ldc + n0 + cb +
+                                                          8 * p) = pk;
+                            }
+                        }
+                        __syncwarp();
+                    }
+                    continue;
+                }
                 const int c_end = min(n_out - c0, a.N - n0 - c0);   // columns of this chunk that exist (may be <= 0)
                 if (m < tl.row_end && c_end > 0) {
                     if (a.out_float) {
@@ -260,25 +305,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                             if (i < c_end) dst[i] = v[i];
                     } else {
                         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.C) + (size_t)m * a.ldc + n0 + c0;
-                        if (c_end >= 32 && ((((size_t)m * a.ldc + n0 + c0) & 7) == 0)) {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[i], v[i + 1]);
-                                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
-                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
-                                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
-                                uint4 pk;
-                                pk.x = *reinterpret_cast<uint32_t*>(&p0);
-                                pk.y = *reinterpret_cast<uint32_t*>(&p1);
-                                pk.z = *reinterpret_cast<uint32_t*>(&p2);
-                                pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                                *reinterpret_cast<uint4*>(dst + i) = pk;
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (i < c_end) dst[i] = __float2bfloat16_rn(v[i]);
-                        }
+                        for (int i = 0; i < 32; ++i)
+                            if (i < c_end) dst[i] = __float2bfloat16_rn(v[i]);
                     }
                 }
             }
@@ -366,7 +395,7 @@ int* tc_error_ptr() {
 
 template <int CTAS>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, cudaStream_t s) {
-    const size_t smem = (size_t)TcShape<CTAS>::STAGES * TcShape<CTAS>::STAGE_BYTES + 1024;
+    const size_t smem = (size_t)TcShape<CTAS>::STAGES * TcShape<CTAS>::STAGE_BYTES + 4 * TC_STRIP_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -427,10 +456,18 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     if (M == 0) return 0;
     const int dual = out_kind == 2;
     const int rows_b = dual ? 2 * N : N;
-    // Rows of B per tile.  With about one row tile per group (decoding with many sequences: the product streams
+    // Rows of B per tile: as many column tiles as the full width would need, but of equal widths (N = 688 with
+    // swiglu: six tiles of 120 gate and 120 up rows instead of five of 128 and one of 48 padded to 128).
+    int n_tile;
+    {
+        const int out_max = dual ? TC_BN / 2 : TC_BN, unit = dual ? 8 : 16;
+        const int tiles = (N + out_max - 1) / out_max;
+        const int out = ((N + tiles - 1) / tiles + unit - 1) / unit * unit;
+        n_tile = dual ? 2 * out : out;
+    }
+    // With about one row tile per group (decoding with many sequences: the product streams
     // the experts' weights once and has G x column tiles to spread over the SMs) narrower tiles can fill a round
     // of SMs where the full width leaves a third of them idle; costs in rows loaded per k-block and round.
-    int n_tile = TC_BN;
     if (group_offsets && (long long)M <= (long long)TC_BM * G) {
         static int sms = 0;
         if (!sms) {
