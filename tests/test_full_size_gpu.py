@@ -8,7 +8,7 @@ import torch
 
 import transformer_b200 as tb
 from plain import llama_moe_plain as P
-from tiny import check_request, n_moe_layers, random_prompts
+from tiny import check_request, random_prompts
 
 pytestmark = pytest.mark.gpu
 

@@ -1,5 +1,4 @@
 """The GGUF reader against files written by the ``gguf`` package (no device)."""
-import os
 
 import numpy as np
 import pytest

@@ -6,7 +6,7 @@ import torch
 
 import transformer_b200 as tb
 from plain import llama_moe_plain as P
-from tiny import BF16_REL_TOL, CONFIGS, make_folder, random_prompts
+from tiny import BF16_REL_TOL, CONFIGS, make_folder
 from transformer_b200.engine.context import StepContext
 from transformer_b200.parts import FEED_FORWARDS, MIXERS, NORMS, POSITIONS, PartSpec
 from transformer_b200.parts.base import WeightedRows

@@ -6,7 +6,6 @@ another in a cache that holds only one batch, so slots and pages are used again 
 in bfloat16, for every tiny configuration.  Every position's logits are compared.
 """
 import pytest
-import torch
 
 from plain import llama_moe_plain as P
 from tiny import CONFIGS, TraceRun, check_request, make_folder, n_moe_layers, random_prompts

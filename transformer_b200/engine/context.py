@@ -15,12 +15,11 @@ The same numbers are kept on the host (``h_*`` lists) for parts that plan on the
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
-from ..cache.slots import PAGE
 
 
 @dataclass

@@ -1,8 +1,6 @@
 """RMSNorm fused with the residual sum (models/llama/common/src/compute.rs:207,275,362)."""
 from __future__ import annotations
 
-import torch
-
 from ..csrc import lib
 from .base import NORMS, Norm, ParamDecl, WeightedRows
 
