@@ -289,6 +289,41 @@ def test_dispatch_grouped_products_and_combine(dtype, E, k, nt, d, di):
         assert float((out.double().cpu() - ref).abs().max()) <= 2 * _tol(dtype, float(ref.abs().max())), use
 
 
+def test_an_expert_that_nearly_every_token_picks():
+    """The decode product sizes a pass by the usual group (one and a half times the mean), so a group far larger
+    than that takes several passes over its weights: every token picks expert 3 and one other expert."""
+    from transformer_b200.parts.linear import gemm_skinny, grouped_matmul
+    lib = _lib()
+    E, k, nt, d, di = 8, 2, 40, 128, 48
+    x, wgu, wd, _ = _grouped_case(torch.bfloat16, E, k, nt, d, di, seed=77)
+    g = torch.Generator().manual_seed(5)
+    other = torch.randint(0, E - 1, (nt,), generator=g)
+    other = other + (other >= 3).long()                          # any expert but 3
+    idx = torch.stack([torch.full((nt,), 3), other], dim=1).to(torch.int32).cuda()
+    idx[::2] = idx[::2].flip(1)                                  # expert 3 is not always the first choice
+    M = nt * k
+    assert int((idx == 3).sum()) == nt and (3 * M // E + 1) // 2 < nt, "one group is larger than a pass"
+    ref = torch.zeros(M, d, dtype=torch.float64)
+    for p in range(M):
+        e = int(idx.view(-1)[p])
+        ref[p] = P.expert_ffn(x[p // k].double().cpu(), wgu[e].double().cpu(), wd[e].double().cpu())
+    tol = 2 * _tol(torch.bfloat16, float(ref.abs().max()))
+    h = torch.empty((M, di), dtype=torch.bfloat16, device="cuda")
+    y = torch.empty((M, d), dtype=torch.bfloat16, device="cuda")
+    pairs = idx.view(-1)
+    assert gemm_skinny(x, wgu, h, groups=E, out_kind=2, max_group_rows=nt, row_group=pairs, x_div=k)
+    assert gemm_skinny(h, wd, y, groups=E, max_group_rows=nt, row_group=pairs)
+    assert float((y.double().cpu() - ref).abs().max()) <= tol, "rows unsorted"
+    off = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    st = torch.empty(M, dtype=torch.int32, device="cuda")
+    pr = torch.empty(M, dtype=torch.int32, device="cuda")
+    lib.call("tb_moe_dispatch", idx.data_ptr(), off.data_ptr(), st.data_ptr(), pr.data_ptr(), M, k, E)
+    h.zero_(), y.zero_()
+    grouped_matmul(x, wgu, h, a_rows=st, group_offsets=off, groups=E, swiglu=True, max_group_rows=nt)
+    grouped_matmul(h, wd, y, group_offsets=off, groups=E, max_group_rows=nt)
+    assert float((y[pr.long()].double().cpu() - ref).abs().max()) <= tol, "rows sorted by expert"
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 16, 8), (8, 50, 24), (9, 129, 104), (33, 688, 4096), (64, 4096, 688), (3, 1000, 72),
                                    (17, 48, 1000)])
 def test_gemm_skinny_dense(M, N, K):

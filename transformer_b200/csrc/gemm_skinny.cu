@@ -233,7 +233,7 @@ static int skinny_launch_shape(const SkinnyArgs& a, cudaStream_t s) {
         dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
         // up to 8 rows and one matrix per group: registers allow twice as many loads in flight per thread
         // (measured in the decode step: -1.5 us per layer on the q-k-v product; for the gate/up pair 4 is best)
-        if (NT == 1 && !DUAL)
+        if constexpr (NT == 1 && !DUAL)
             TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, 8>), grid, WK * WN * 32, 0, s, a);
         else
             TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR>), grid, WK * WN * 32, 0, s, a);
@@ -270,7 +270,15 @@ int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y
     if (M == 0) return 0;
     SkinnyArgs a{(const __nv_bfloat16*)X, x_rows, (const __nv_bfloat16*)W, Y, group_offsets, w_group_stride,
                  ldx, ldw, ldy, M, N, K, G, row_group, x_div, w_constant};
-    const int rows = (max_group_rows > 0 && max_group_rows < M) ? max_group_rows : M;
+    int rows = (max_group_rows > 0 && max_group_rows < M) ? max_group_rows : M;
+    if (G > 1) {
+        // A pass takes 8, 16 or 32 rows of a group and a thread's registers are sized by the pass (with 16 rows the
+        // gate/up kernel fits one block on an SM instead of two).  So the pass is sized by what most groups hold,
+        // one and a half times the mean, not by the largest group there could be: a group with more rows takes
+        // another pass over its weights, which come from L2 that time.  (Decode steps of 12 to 32 sequences: 4..10 %.)
+        const long long usual = (3ll * M / G + 1) / 2;
+        if (usual < rows) rows = usual < 1 ? 1 : (int)usual;
+    }
     if (rows <= 8) return skinny_launch_nt<1>(a, out_kind, s);
     if (rows <= 16) return skinny_launch_nt<2>(a, out_kind, s);
     return skinny_launch_nt<4>(a, out_kind, s);
