@@ -88,13 +88,36 @@ def _error_text(code: int) -> str:
 
 launch_count = 0     # launchers called so far (a launcher may start more than one kernel)
 
+_scope_stream = None  # inside stream_scope(): the handle of the stream that was current at its start
+
+
+class stream_scope:
+    """``with stream_scope():`` looks torch's current stream up once for all the launches inside (a model's forward
+    pass is some hundred launches, and the look-up costs as much as a launch).  Whoever opens it must not
+    change the current stream inside; a scope opened inside a graph capture sees the capturing stream."""
+
+    def __enter__(self):
+        global _scope_stream
+        self._before = _scope_stream
+        _scope_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _scope_stream
+        _scope_stream = self._before
+        return False
+
+
+def _stream() -> int:
+    return _scope_stream if _scope_stream is not None else torch.cuda.current_stream().cuda_stream
+
 
 def try_call(name: str, *args) -> bool:
     """Like :func:`call`, but a kernel that refuses the sizes (TB_ERR_UNSUPPORTED) answers False
     instead of raising, so the caller can take the general kernel."""
     global launch_count
-    fn = getattr(library(), name)
-    rc = fn(*args, torch.cuda.current_stream().cuda_stream)
+    fn = getattr(_lib if _lib is not None else library(), name)
+    rc = fn(*args, _stream())
     if rc == -2:
         return False
     if rc != 0:
@@ -107,8 +130,8 @@ def call(name: str, *args) -> None:
     """Launch ``name`` on torch's current stream."""
     global launch_count
     launch_count += 1
-    fn = getattr(library(), name)
-    rc = fn(*args, torch.cuda.current_stream().cuda_stream)
+    fn = getattr(_lib if _lib is not None else library(), name)
+    rc = fn(*args, _stream())
     if rc != 0:
         raise KernelError(f"{name}: {_error_text(rc)}")
 

@@ -238,6 +238,10 @@ class Engine:
         return self._forward(ctx, logits_out)
 
     def _forward(self, ctx: StepContext, logits_out=None) -> torch.Tensor:
+        with lib.stream_scope():       # also inside a capture: the scope then holds the capturing stream
+            return self._forward_on_stream(ctx, logits_out)
+
+    def _forward_on_stream(self, ctx: StepContext, logits_out=None) -> torch.Tensor:
         nt, d, V = ctx.nt, self.spec.width, self.spec.vocab
         sfx = lib.suffix(self.dtype)
         x = ctx.scratch("stream", (nt, d), torch.float32)
