@@ -9,7 +9,8 @@ from .config import ConfigError, LlamaMeta, register_architecture
 from .engine import Engine, StepError, generate, GenerationResult
 from .sampling import SampleArgs, SampleArgsError
 from .cache import CacheError
+from .csrc.lib import KernelError
 from .weights import WeightError
 
 __all__ = ["load", "random_model", "write_random_model", "read_config", "parse_dtype", "Engine", "LlamaMeta", "generate", "GenerationResult", "SampleArgs", "SampleArgsError",
-           "ConfigError", "WeightError", "CacheError", "StepError", "register_architecture"]
+           "ConfigError", "WeightError", "CacheError", "StepError", "KernelError", "register_architecture"]

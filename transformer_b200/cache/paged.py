@@ -101,6 +101,9 @@ class Cache:
     def extend(self, slot: int, new_tokens: int) -> int:
         return self.table.extend(slot, new_tokens)
 
+    def truncate(self, slot: int, length: int) -> None:
+        self.table.truncate(slot, length)
+
     def length(self, slot: int) -> int:
         return self.table.length[slot]
 

@@ -100,6 +100,19 @@ class SequenceTable:
         self.length[slot] = total
         return start
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forget the sequence's tokens from position ``length`` on and give back the pages that then hold
+        nothing (a step that failed after :meth:`extend` puts the sequence back to where it was)."""
+        if slot not in self.length:
+            raise CacheError(f"slot {slot} is not open")
+        if not (0 <= length <= self.length[slot]):
+            raise CacheError(f"slot {slot} holds {self.length[slot]} tokens; cannot truncate to {length}")
+        keep = (length + PAGE - 1) // PAGE
+        pl = self.page_list[slot]
+        while len(pl) > keep:
+            self.pages.give_back(pl.pop())
+        self.length[slot] = length
+
     def check(self) -> None:
         self.slots.check()
         self.pages.check()

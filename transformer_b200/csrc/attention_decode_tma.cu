@@ -296,7 +296,7 @@ extern "C" int tb_attention_decode_tma_bf16(const void* q, void* out, const void
     if (nt <= 0) return nt == 0 ? 0 : TB_ERR_ARG;
     int rc = 0;
     int* err = tc_error_ptr();
-    if (!err) return TB_ERR_UNSUPPORTED;
+    if (!err) return tb_last_error();
     DecodeTmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, tok_seq, tok_pos, page_table, partial, done, err,
                     max_pages, q_stride, nh, nkvh, splits, 0, scale * 1.4426950408889634f};
     const int group = nh / nkvh;

@@ -371,7 +371,7 @@ int tb_attention_tc_bf16(const void* q, void* out, const void* kc, const void* v
     rc = make_map(&mv, vc, rows, dh, dh, AT_BN);
     if (rc) return rc;
     int* err_ptr = tc_error_ptr();
-    if (!err_ptr) return TB_ERR_UNSUPPORTED;
+    if (!err_ptr) return tb_last_error();
     AtArgs a{(__nv_bfloat16*)out, tile_seq, tile_t0, tile_nq, tok_pos, page_table, err_ptr, tiles, max_pages, nh, nkvh,
              scale * 1.4426950408889634f, (unsigned)(AT_BN * 128), 1024u};
     return dh == 64 ? attention_tc_launch<64>(mq, mk, mv, a, s) : attention_tc_launch<128>(mq, mk, mv, a, s);

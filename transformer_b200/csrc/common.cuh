@@ -135,6 +135,20 @@ __device__ __forceinline__ void pdl_sync() {
 // that a kernel with a large ring asked for stays in force, and the kernels after it run with a sliver
 // of L1 (measured: a decode step of small kernels lost a third of its speed behind one 200 KB kernel).
 // Looked up per kernel, set again only when a launch needs more than any before it.
+// A CUDA call of a launcher's set-up that failed (an attribute query, an attribute that was refused) is kept here
+// until the launcher returns: tb_last_error() hands it out before anything else, so it reaches the caller as the
+// launcher's result instead of vanishing.  One word per host thread, shared by all files of the library.
+inline int& tb_pending_error() {
+    static thread_local int code = 0;
+    return code;
+}
+static inline void tb_note_error(cudaError_t e) {
+    if (e != cudaSuccess) {
+        cudaGetLastError();   // the runtime's own copy would otherwise be blamed on a later, innocent call
+        if (!tb_pending_error()) tb_pending_error() = (int)e;
+    }
+}
+
 static inline void tb_state_carveout(const void* kernel, unsigned threads, size_t dyn_smem) {
     struct Seen { const void* kernel; size_t need; };
     static Seen seen[128];
@@ -152,7 +166,14 @@ static inline void tb_state_carveout(const void* kernel, unsigned threads, size_
     }
     seen[at].need = dyn_smem;
     cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) { cudaGetLastError(); return; }
+    {
+        const cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+        if (e != cudaSuccess) {
+            seen[at].need = 0;    // not stated: the next launch tries again
+            tb_note_error(e);
+            return;
+        }
+    }
     const unsigned warps = (threads + 31) / 32;
     const unsigned regs_per_warp = ((unsigned)fa.numRegs * 32 + 255) / 256 * 256;
     unsigned blocks = 2048 / (warps * 32);
@@ -164,7 +185,7 @@ static inline void tb_state_carveout(const void* kernel, unsigned threads, size_
     if (want > sm_total) want = sm_total / per_block ? sm_total / per_block * per_block : per_block;
     int pct = (int)((want * 100 + sm_total - 1) / sm_total);
     pct = pct < 12 ? 12 : pct > 100 ? 100 : pct;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, pct) != cudaSuccess) cudaGetLastError();
+    tb_note_error(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, pct));
 }
 
 template <typename... KArgs, typename... Args>
@@ -186,4 +207,8 @@ static inline void tb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block
 #define TB_LAUNCH(kernel, grid, block, smem, stream, ...) \
     tb_launch_pdl(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
 
-static inline int tb_last_error() { return (int)cudaGetLastError(); }
+static inline int tb_last_error() {
+    const int launch = (int)cudaGetLastError(), pending = tb_pending_error();
+    tb_pending_error() = 0;
+    return pending ? pending : launch;
+}

@@ -66,6 +66,15 @@ __device__ __forceinline__ uint4 ld16w(const __nv_bfloat16* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+// The same stream of W when W is itself a result of the step (the router product with the roles swapped reads the
+// normalized activations as W): the read-only path promises that nothing writes the data during the kernel's
+// lifetime, which does not hold while the kernel before this one may still be draining, so the plain path is taken.
+__device__ __forceinline__ uint4 ld16s(const __nv_bfloat16* p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
     return *reinterpret_cast<const uint4*>(p);
 }
@@ -169,11 +178,20 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
                 const int k = (s0 + u * WK) * 32;
                 const bool live = k + t * 8 < a.K;      // also false past the last step
                 if (!have) {
-                    wa[u] = live ? ld16w(w0 + k) : zero4;
-                    wb[u] = live ? ld16w(w1 + k) : zero4;
-                    if (DUAL) {
-                        ua[u] = live ? ld16w(u0 + k) : zero4;
-                        ub[u] = live ? ld16w(u1 + k) : zero4;
+                    if (a.w_constant) {
+                        wa[u] = live ? ld16w(w0 + k) : zero4;
+                        wb[u] = live ? ld16w(w1 + k) : zero4;
+                        if (DUAL) {
+                            ua[u] = live ? ld16w(u0 + k) : zero4;
+                            ub[u] = live ? ld16w(u1 + k) : zero4;
+                        }
+                    } else {
+                        wa[u] = live ? ld16s(w0 + k) : zero4;
+                        wb[u] = live ? ld16s(w1 + k) : zero4;
+                        if (DUAL) {
+                            ua[u] = live ? ld16s(u0 + k) : zero4;
+                            ub[u] = live ? ld16s(u1 + k) : zero4;
+                        }
                     }
                 }
 #pragma unroll

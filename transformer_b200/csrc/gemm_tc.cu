@@ -389,7 +389,13 @@ static __device__ int tc_error_word;
 
 int* tc_error_ptr() {
     static int* p = nullptr;
-    if (!p && cudaGetSymbolAddress((void**)&p, tc_error_word) != cudaSuccess) p = nullptr;
+    if (!p) {
+        const cudaError_t e = cudaGetSymbolAddress((void**)&p, tc_error_word);
+        if (e != cudaSuccess) {
+            p = nullptr;
+            tb_note_error(e);     // the launcher that asked returns this code
+        }
+    }
     return p;
 }
 
@@ -426,8 +432,13 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, cud
             int n = 0;
             cfg.gridDim = dim3(sms > 1 ? sms / 2 * 2 : 2);
             cfg.numAttrs = 2;
-            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<CTAS>, &cfg) != cudaSuccess || n <= 0) {
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<CTAS>, &cfg);
+            if (e != cudaSuccess) {
                 cudaGetLastError();
+                max_units = 0;                 // asked again at the next launch
+                return (int)e;                 // a failed query is an error, not "no room"
+            }
+            if (n <= 0) {
                 max_units = 0;
                 return TB_ERR_UNSUPPORTED;     // no room for a pair of these blocks on this device
             }
@@ -493,7 +504,7 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     rc = make_map(&mb, B, (long long)G * rows_b, K, ldb, n_tile / 2);     // a box is half of the B tile
     if (rc) return rc;
     int* err_ptr = tc_error_ptr();
-    if (!err_ptr) return TB_ERR_UNSUPPORTED;
+    if (!err_ptr) return tb_last_error();
     // pairs of blocks pay from about a thousand rows per group on (see the head of this file)
     const bool pair = (long long)M >= 1024ll * G;
     TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, 0, n_tile};
@@ -509,6 +520,14 @@ int tb_gemm_tc_status() {
     if (cudaMemcpyFromSymbol(&v, tc_error_word, sizeof(int)) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(tc_error_word, &zero, sizeof(int));
     return v;
+}
+
+// The same word copied to `host_dst` (pinned host memory) in stream order, without waiting: it arrives with
+// whatever else the caller reads back from that stream, and is not cleared.
+int tb_kernel_status_async(int* host_dst, cudaStream_t s) {
+    int* p = tc_error_ptr();
+    if (!p) return tb_last_error();
+    return (int)cudaMemcpyAsync(host_dst, p, sizeof(int), cudaMemcpyDeviceToHost, s);
 }
 
 int tb_gather_rows_bf16(const void* x, const int* rows, void* out, int M, int d, cudaStream_t s) {

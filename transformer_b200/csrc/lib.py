@@ -39,6 +39,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_moe_dispatch": "ppppiii", "tb_topk_softmax": "pllppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
     "tb_sample": "plpiififpp",
+    "tb_kernel_status_async": "p",
 }
 _NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
@@ -153,9 +154,41 @@ def attention_tile_tokens(nh: int, nkvh: int) -> int:
 
 
 def gemm_tc_status() -> int:
-    """0, or the code of a tensor-core product that gave up on a wait since the last call
-    (synchronises the device)."""
+    """0, or the code of a kernel with bounded waits (the tensor-core products, the tensor-core and the
+    page-ring attention) that gave up on a wait since the last call; synchronises the device and clears it."""
     return library().tb_gemm_tc_status()
+
+
+def kernel_status_async(host_int32: torch.Tensor) -> None:
+    """Copy the same code into the first element of a pinned int32 host tensor, in stream order and without
+    waiting: it lands together with the step's other results."""
+    rc = library().tb_kernel_status_async(host_int32.data_ptr(), _stream())
+    if rc != 0:
+        raise KernelError(f"tb_kernel_status_async: {_error_text(rc)}")
+
+
+def _gave_up(code: int) -> str:
+    """Which kernel family a wait code belongs to (1..5 tensor-core products, 11..17 tensor-core prompt
+    attention, 21..22 decode attention with the page ring)."""
+    if 1 <= code <= 5:
+        return "tensor-core matrix product"
+    if 11 <= code <= 17:
+        return "tensor-core prompt attention"
+    if 21 <= code <= 22:
+        return "decode attention"
+    return "unknown kernel"
+
+
+def raise_for_status(code: int, recover=None) -> None:
+    """``code`` is the word the kernels with bounded waits share (0: all well).  Anything else means that a wait
+    ran out and the kernel returned early: its result is not to be used.  ``recover()`` is called first (it puts
+    back what such a kernel leaves behind), then :class:`KernelError` is raised."""
+    if not code:
+        return
+    if recover is not None:
+        recover()
+    raise KernelError(f"a kernel gave up after its wait limit (code {code}: {_gave_up(int(code))}); the results of "
+                      f"the steps since the last check are not valid")
 
 
 def attention_prefill_tile_tokens() -> int:

@@ -14,8 +14,9 @@ The same numbers are kept on the host (``h_*`` lists) for parts that plan on the
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass
-from typing import Dict, Optional, Sequence, Tuple
+from typing import Callable, Dict, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -30,12 +31,27 @@ class AttentionTiles:
     count: int
 
 
+def weak_callback(method) -> Callable[[], None]:
+    """A plain function that calls the bound method ``method`` for as long as its object lives and does nothing
+    afterwards.  An object that hands one of its own methods to something it owns would otherwise keep itself
+    alive through that something (a reference cycle), and would be freed only when the cyclic collector next runs:
+    at an arbitrary allocation, possibly in the middle of someone else's CUDA graph capture."""
+    ref = weakref.WeakMethod(method)
+
+    def call() -> None:
+        m = ref()
+        if m is not None:
+            m()
+    return call
+
+
 class Workspace:
     """Named scratch buffers, kept between steps and grown when a step needs more."""
 
     def __init__(self, device, on_grow=None):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._kept_zero = set()  # keys of the buffers whose users leave them zeroed
         self.frozen = False     # set while a CUDA graph is being captured
         self.on_grow = on_grow  # called before a buffer is replaced (whoever kept its address must forget it)
 
@@ -54,7 +70,18 @@ class Workspace:
                 self.on_grow()
             buf = (torch.zeros if zero else torch.empty)(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            if zero:
+                self._kept_zero.add(key)
         return buf[:n].view(*shape)
+
+    def rezero(self) -> None:
+        """Zero again the buffers that their users are trusted to leave zeroed (after a kernel returned early)."""
+        for key in self._kept_zero:
+            self._bufs[key].zero_()
+
+    def clear(self) -> None:
+        self._bufs.clear()
+        self._kept_zero.clear()
 
     @property
     def nbytes(self) -> int:

@@ -12,6 +12,7 @@ are always float, and nothing inside synchronises with the host.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -23,7 +24,7 @@ from ..parts.block import Layer, resolve
 from ..parts.base import NORMS
 from ..parts.linear import matmul_nt
 from ..parts.spec import ModelSpec
-from .context import StepContext, Workspace
+from .context import StepContext, Workspace, weak_callback
 
 
 class StepError(ValueError):
@@ -51,7 +52,9 @@ class Engine:
         self.cache = Cache([m.cache_need() for m in mixers], [m.state_need() for m in mixers],
                            [e.cache_of for e in runs], max_tokens=max_tokens, max_context=spec.max_context,
                            max_slots=max_slots, dtype=dtype, device=device)
-        self.workspace = Workspace(device, on_grow=self._drop_graphs)
+        # weak: the workspace must not keep its owner alive (see weak_callback); an engine that goes out of scope
+        # is freed at once, by reference count, and its CUDA graphs with it
+        self.workspace = Workspace(device, on_grow=weak_callback(self._drop_graphs))
         self._identity_tables = {}
         self.recorder = None    # callable(name, run index, tensor copy) for debugging; see StepContext.record
         self._tile_sizes = sorted({int(t) for m in mixers for t in getattr(m, "tile_sizes", ())})
@@ -83,6 +86,30 @@ class Engine:
             torch.cuda.synchronize(self.device)
         self._graphs.clear()
         self._graph_seen.clear()
+
+    def release(self) -> None:
+        """Give up the captured graphs and the scratch memory now (the weights and the cache go when the last
+        reference to the engine goes).  Call it outside any CUDA graph capture; the engine can still step
+        afterwards and captures again.  An engine that is simply dropped does the same through its reference
+        count: nothing of it waits for Python's cyclic collector."""
+        self._drop_graphs()
+        self.workspace.clear()
+        self._identity_tables.clear()
+
+    def check_kernels(self, code: Optional[int] = None) -> None:
+        """Raise :class:`~transformer_b200.csrc.lib.KernelError` if a kernel with bounded waits gave up since the
+        last check (such a kernel returns early and leaves a half-written result).  ``code``: the status word if
+        the caller has fetched it already (``lib.kernel_status_async``); else it is read now, which waits for
+        the device.  Before raising, the counters that the kernels are trusted to leave at zero are zeroed again,
+        so the steps after the error are sound."""
+        if code is None:
+            code = lib.gemm_tc_status()
+        lib.raise_for_status(code, self._after_gave_up)
+
+    def _after_gave_up(self) -> None:
+        torch.cuda.synchronize(self.device)
+        lib.gemm_tc_status()          # clears the word
+        self.workspace.rezero()
 
     def staging(self, n_ints: int):
         """A pinned host buffer, the device buffer it is copied to, and the event of its last copy."""
@@ -119,6 +146,10 @@ class Engine:
         device_tokens: for one-token steps, an int32 device tensor [B] that holds the tokens (for
         instance what the sampler just wrote); ``tokens`` then only gives the shape.  Nothing comes
         back to the host between such steps.
+
+        The logits of a one-token step may lie in memory that the next such step of the same batch size writes
+        again (a replayed CUDA graph has one fixed output): use or copy them before stepping on.  A step that
+        raises leaves the sequences as they were before it.
         """
         B = len(slots)
         if len(tokens) != B:
@@ -140,6 +171,10 @@ class Engine:
             for w in want[b]:
                 if not (0 <= int(w) < n):
                     raise StepError(f"wanted place {w} lies outside the {n} tokens of sequence {b}")
+        n_total = sum(len(t) for t in tokens)
+        one_each = n_total == B and all(list(w) == [0] for w in want)
+        if device_tokens is not None and not one_each:
+            raise StepError("device_tokens serve steps of one token per sequence that want its logits")
         # room for everything first: a step either runs whole or not at all
         need = sum(self.cache.table.pages_needed(s, len(t)) for s, t in zip(slots, tokens))
         if need > self.cache.table.pages.free:
@@ -147,21 +182,24 @@ class Engine:
         for s, t in zip(slots, tokens):
             if self.cache.length(s) + len(t) > self.spec.max_context:
                 raise CacheError(f"slot {s} would exceed the context of {self.spec.max_context}")
-        pos0 = [self.cache.extend(s, len(t)) for s, t in zip(slots, tokens)]
-
-        n_total = sum(len(t) for t in tokens)
-        if n_total == B and all(list(w) == [0] for w in want) and \
-                (device_tokens is not None or (self.use_graphs and B <= self.graph_max_batch)):
-            return self._run_decode(slots, tokens, pos0, device_tokens)
-        if device_tokens is not None:
-            raise StepError("device_tokens serve steps of one token per sequence that want its logits")
-        if n_total <= self.max_step_tokens:
-            rows, base = [], 0
-            for b in range(B):
-                rows.extend(base + int(w) for w in want[b])
-                base += len(tokens[b])
-            return self._run(slots, tokens, pos0, rows)
-        return self._run_in_pieces(slots, tokens, pos0, want)
+        before = [self.cache.length(s) for s in slots]
+        try:
+            pos0 = [self.cache.extend(s, len(t)) for s, t in zip(slots, tokens)]
+            if one_each and (device_tokens is not None or (self.use_graphs and B <= self.graph_max_batch)):
+                return self._run_decode(slots, tokens, pos0, device_tokens)
+            if n_total <= self.max_step_tokens:
+                rows, base = [], 0
+                for b in range(B):
+                    rows.extend(base + int(w) for w in want[b])
+                    base += len(tokens[b])
+                return self._run(slots, tokens, pos0, rows)
+            return self._run_in_pieces(slots, tokens, pos0, want)
+        except BaseException:
+            # nothing of a failed step stays: the sequences are as long as before it, their new pages are free
+            for s, n in zip(slots, before):
+                if self.cache.length(s) > n:
+                    self.cache.truncate(s, n)
+            raise
 
     def _run_in_pieces(self, slots, tokens, pos0, want) -> torch.Tensor:
         """A step larger than the scratch memory allows runs as consecutive pieces of the token
@@ -220,10 +258,18 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             before = lib.launch_count
             self.workspace.frozen = True      # scratch must not move while it is being captured
+            # Nothing may destroy a CUDA graph while this one is captured (that invalidates the capture).  Python
+            # frees garbage that sits in reference cycles at arbitrary allocations, and such garbage may own graphs
+            # (another engine, anything of torch's): free it now, and keep the collector off until the capture ends.
+            gc.collect()
+            collecting = gc.isenabled()
+            gc.disable()
             try:
-                with torch.cuda.graph(graph):
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                     self._forward(ctx, logits)
             finally:
+                if collecting:
+                    gc.enable()
                 self.workspace.frozen = False
             entry = (graph, logits, lib.launch_count - before)
             lib.launch_count = before

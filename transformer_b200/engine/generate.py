@@ -207,9 +207,14 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[in
     if sampler is None:
         sampler = engine._sampler = Sampler(engine.device)
 
-    pinned = getattr(engine, "_token_landing", None)     # two pinned buffers: at most two steps are in flight
+    from ..csrc import lib
+
+    # two pinned buffers (at most two steps are in flight): the step's tokens, and in the last element the word
+    # that a kernel sets when it gave up on a bounded wait
+    n_land = max(1, table.max_slots)
+    pinned = getattr(engine, "_token_landing", None)
     if pinned is None:
-        pinned = engine._token_landing = [torch.empty(max(1, table.max_slots), dtype=torch.int32, pin_memory=True)
+        pinned = engine._token_landing = [torch.zeros(n_land + 1, dtype=torch.int32, pin_memory=True)
                                           for _ in range(2)]
     turn = [0]
 
@@ -229,6 +234,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[in
         host = pinned[turn[0] % 2]
         turn[0] += 1
         host[:len(reqs)].copy_(ids, non_blocking=True)   # the one device-to-host read of the step (infer.rs:140-146)
+        lib.kernel_status_async(host[n_land:])           # and four bytes beside it: did every kernel finish its work?
         done = torch.cuda.Event()
         done.record()
         return Launched(list(reqs), (ids, host, done))
@@ -236,6 +242,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_steps: Optional[in
     def collect(step):
         _, host, done = step.payload
         done.synchronize()
+        engine.check_kernels(int(host[n_land]))          # raises if a kernel returned early: no token of it is used
         return host[:len(step.reqs)].tolist()
 
     out, why, timing = run_batches(batches, prompts, limit, stops, spec.max_context, open_slot=engine.open,
