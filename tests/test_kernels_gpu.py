@@ -561,3 +561,41 @@ def test_attention_decode_tma(nh, nkvh, dh):
             assert int(done.abs().sum()) == 0 and lib.gemm_tc_status() == 0
     c48 = attention_case([1], [10], 2, 1, 48, torch.bfloat16, 1, seed=1)
     assert _run_attention(lib, c48, torch.bfloat16, 1, decode=True, tma=True) is None, "a head of 48 is refused"
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_random_fill_is_the_rule_bit_for_bit(dtype):
+    """The fill kernel against the tests' own restatement of the rule (plain/counter_weights.py), at sizes with
+    tails, at an odd offset into the stream, into a tensor that does not start on a 16-byte boundary."""
+    from plain import counter_weights as C
+    from transformer_b200.weights import counter_random as R
+    lib = _lib()
+    for seed, name, n, first, std in ((0, "token_embd.weight", 1, 0, 0.02), (3, "blk.1.attn_qkv.weight", 8 * 257 + 5, 0, 0.02),
+                                      (2 ** 33 + 1, "output.weight", 100003, 77, 1.0), (9, "x", 4096, 2 ** 33 + 3, 0.5)):
+        buf = torch.full((n + 3,), 7.0, dtype=dtype, device="cuda")
+        out = buf[1:1 + n]                                   # misaligned for 16-byte stores: the scalar path
+        lib.call("tb_random_fill_" + lib.suffix(dtype), out.data_ptr(), n, R.stream_base(seed, name), first,
+                 float(R.scale_for(std)))
+        want = C.values(seed, name, (n,), std, dtype=dtype, first=first)
+        assert torch.equal(out.float().cpu(), want), (seed, name, n)
+        assert float(buf[0]) == 7.0 and float(buf[n + 1]) == 7.0, "wrote outside its range"
+        whole = torch.empty(n, dtype=dtype, device="cuda")
+        lib.random_fill(whole, R.stream_base(seed, name), float(R.scale_for(std)), first)
+        assert torch.equal(whole.float().cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_weights_drawn_on_the_device_are_the_folders(dtype, tmp_path):
+    import transformer_b200 as tb
+    from tiny import CONFIGS
+    cfg, seed = CONFIGS["B"]
+    on_device = tb.random_model(cfg, seed=seed, dtype=dtype, std=0.1, max_tokens=64)
+    from_file = tb.load(tb.write_random_model(str(tmp_path / "m"), cfg, seed=seed, dtype=dtype, std=0.1), dtype=dtype,
+                        max_tokens=64)
+    assert torch.equal(on_device.embedding, from_file.embedding) and torch.equal(on_device.head, from_file.head)
+    assert on_device.head.data_ptr() == on_device.embedding.data_ptr(), "a tied head shares the table's storage"
+    for a, b in zip(on_device.layers, from_file.layers):
+        for name, part in a.parts().items():
+            for wname, w in part.weights.items():
+                assert torch.equal(w, b.parts()[name].weights[wname]), (name, wname)

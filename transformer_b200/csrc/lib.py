@@ -18,8 +18,8 @@ import torch
 
 from .build import KernelBuildError, ensure_built
 
-_P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
-_CODES = {"p": _P, "i": _I, "f": _F, "l": _L}
+_P, _I, _F, _L, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_ulonglong
+_CODES = {"p": _P, "i": _I, "f": _F, "l": _L, "u": _U}
 
 # name -> argument codes (the trailing stream is added for all but the ones marked no_stream)
 _SIGNATURES: Dict[str, str] = {
@@ -40,6 +40,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
     "tb_sample": "plpiififpp",
     "tb_kernel_status_async": "p",
+    "tb_random_fill_f32": "plulf", "tb_random_fill_bf16": "plulf",
 }
 _NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
@@ -147,6 +148,14 @@ def suffix(dtype: torch.dtype) -> str:
     if dtype == torch.bfloat16:
         return "bf16"
     raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
+
+
+def random_fill(t: torch.Tensor, base: int, scale: float, first: int = 0) -> None:
+    """Fill the contiguous tensor ``t`` (float32 or bfloat16) with elements first .. first + t.numel() - 1 of the
+    counter-based stream that starts at ``base`` (see weights/counter_random.py)."""
+    if not t.is_contiguous():
+        raise KernelError("random_fill needs a contiguous tensor")
+    call("tb_random_fill_" + suffix(t.dtype), t.data_ptr(), t.numel(), int(base), int(first), float(scale))
 
 
 def attention_tile_tokens(nh: int, nkvh: int) -> int:
