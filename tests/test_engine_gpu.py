@@ -10,7 +10,8 @@ import torch
 
 import transformer_b200 as tb
 from plain import llama_moe_plain as P
-from tiny import BF16_REL_TOL, CONFIGS, FP32_TOL, ROOT, check_request, make_folder, n_moe_layers, random_prompts
+from tiny import (BF16_REL_TOL, CONFIGS, FP32_TOL, ROOT, check_generation, check_request, make_folder, n_moe_layers,
+                  random_prompts)
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
@@ -107,23 +108,31 @@ def test_a_slot_used_again_sees_nothing_of_its_past(dtype, folders):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_a_step_cut_into_pieces_changes_nothing(dtype, folders):
+    """Config C reaches the tensor-core prompt kernels in bfloat16 (attention with heads of 64, grouped expert
+    products): whole against pieces, and both paths against the plain implementation at every wanted place."""
     cfg, _ = CONFIGS["C"]
     _, tensors = P.read_folder(folders["C"])
     prompts = random_prompts(cfg["vocab_size"], [90, 33, 150], seed=8)
     whole = tb.load(folders["C"], dtype=dtype, max_tokens=512)
     pieces = tb.load(folders["C"], dtype=dtype, max_tokens=512, max_step_tokens=64)   # 273 tokens: 5 pieces
     outs = []
+    want = [[0, len(p) // 2, len(p) - 1] for p in prompts]
+    rec = Recorder(whole)
     for eng in (whole, pieces):
         slots = [eng.open() for _ in prompts]
-        want = [[0, len(p) // 2, len(p) - 1] for p in prompts]
         outs.append(eng.step(slots, prompts, want).cpu())
+        if eng is whole:
+            routes = torch.stack(rec.take())             # [layers, 273, k]
+            whole.recorder = None
         outs.append(eng.step(slots, [[3], [4], [5]]).cpu())
     tol = 1e-5 if dtype == "float32" else BF16_REL_TOL * float(outs[0].abs().max())
     assert float((outs[0] - outs[2]).abs().max()) <= tol
     assert float((outs[1] - outs[3]).abs().max()) <= tol
-    ref = torch.stack([P.forward(cfg, tensors, p, want=[0, len(p) // 2, len(p) - 1]) for p in prompts]).reshape(9, -1)
-    if dtype == "float32":
-        assert float((outs[2] - ref).abs().max()) <= FP32_TOL
+    base = 0
+    for i, p in enumerate(prompts):
+        got = {w: outs[0][3 * i + j] for j, w in enumerate(want[i])}
+        check_request(cfg, tensors, p, got, routes[:, base:base + len(p)].numpy(), dtype, f"whole step, request {i}")
+        base += len(p)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -170,25 +179,6 @@ def test_step_refuses_bad_input_and_changes_nothing(folders):
 
 
 # ---------------------------------------------------------------------------------------------
-def _plain_follow(cfg, tensors, prompt, got, dtype, args=None, us=None):
-    """Check generated tokens against the plain implementation, teacher-forced on the engine's own
-    tokens: greedy -> the token's plain logit is the maximum, up to the rounding rule of the path;
-    sampled -> the token is the one whose interval of the plain distribution holds u."""
-    seq = list(prompt)
-    for j, tok in enumerate(got):
-        logits = P.forward(cfg, tensors, seq, want=[len(seq) - 1])[0]
-        if args is None or args.greedy:
-            slack = 2 * (FP32_TOL if dtype == "float32" else BF16_REL_TOL * float(logits.abs().max()))
-            assert float(logits[tok]) >= float(logits.max()) - slack, f"token {j}: {tok} is not the plain argmax"
-        else:
-            kept, probs = P.sample_distribution(logits, args.temperature, args.top_k, args.top_p)
-            assert tok in kept
-            lo = sum(probs[:kept.index(tok)])
-            eps = 1e-3 if dtype == "float32" else 5e-2
-            assert lo - eps <= us[j] <= lo + probs[kept.index(tok)] + eps, f"token {j}: u = {us[j]} misses {tok}"
-        seq.append(tok)
-
-
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "dense"])
 def test_greedy_generation_through_the_entry_point(name, dtype, folders):
@@ -198,8 +188,7 @@ def test_greedy_generation_through_the_entry_point(name, dtype, folders):
     engine = tb.load(folders[name], dtype=dtype, max_tokens=256)
     res = tb.generate(engine, prompts, max_steps=8, stop_tokens=(), max_batch=3)     # two batches, slots reused
     assert res.batches == [[0, 1, 2], [3, 4]] and all(len(t) == 8 for t in res.tokens)
-    for p, got in zip(prompts, res.tokens):
-        _plain_follow(cfg, tensors, p, got, dtype)
+    check_generation(engine, cfg, tensors, prompts, res.tokens, res.batches, dtype)
     if dtype == "float32":
         assert res.tokens == [P.greedy_generate(cfg, tensors, p, 8) for p in prompts]
     assert engine.cache.table.slots.held == 0 and engine.cache.table.pages.held == 0
@@ -230,14 +219,15 @@ def test_published_workloads(dtype, tmp_path):
     _, tb_ = P.read_folder(fb)
     ea = tb.load(fa, dtype=dtype, max_tokens=256)
     pa = random_prompts(ca["vocab_size"], [5, 11, 17], seed=1)
-    for p, got in zip(pa, tb.generate(ea, pa, max_steps=8, stop_tokens=()).tokens):
-        _plain_follow(ca, ta, p, got, dtype)
+    res = tb.generate(ea, pa, max_steps=8, stop_tokens=())
+    check_generation(ea, ca, ta, pa, res.tokens, res.batches, dtype)
     eb = tb.load(fb, dtype=dtype, max_tokens=512)
     pb = random_prompts(cb["vocab_size"], [1, 9, 30, 64], seed=3)
     args = tb.SampleArgs(temperature=0.8)
-    together = tb.generate(eb, pb, max_steps=12, sample_args=args, seed=4, stop_tokens=()).tokens
-    for r, (p, got) in enumerate(zip(pb, together)):
-        _plain_follow(cb, tb_, p, got, dtype, args, [uniform(4, r, j) for j in range(12)])
+    res = tb.generate(eb, pb, max_steps=12, sample_args=args, seed=4, stop_tokens=())
+    together = res.tokens
+    check_generation(eb, cb, tb_, pb, together, res.batches, dtype,
+                     sample=(args, {r: [uniform(4, r, j) for j in range(12)] for r in range(4)}))
     assert together == tb.generate(eb, pb, max_steps=12, sample_args=args, seed=4, stop_tokens=()).tokens, "repeatable"
     assert together != tb.generate(eb, pb, max_steps=12, sample_args=args, seed=5, stop_tokens=()).tokens
 
@@ -348,3 +338,65 @@ def test_looking_ahead_changes_no_token(dtype, folders):
         assert ahead.timing.decode_tokens == strict.timing.decode_tokens
     engine.cache.table.check()
     assert engine.cache.table.slots.free == 3
+
+
+# ---------------------------------------------------------------------------------------------
+def _decode_batch(engine, prompts, feeds, steps):
+    slots = [engine.open() for _ in prompts]
+    engine.step(slots, prompts)
+    outs = [engine.step(slots, [[f[j]] for f in feeds]).cpu().clone() for j in range(steps)]
+    for s in slots:
+        engine.close(s)
+    return outs
+
+
+@pytest.mark.parametrize("n", [24, 64])
+def test_wide_bfloat16_decode_batches_through_graphs(n, folders):
+    """A decode step of 24 or 64 sequences is a captured graph whose dense products (more than 16 rows) are library
+    calls.  Without experts (no near-ties to fall either way) every sequence's logits are held against the plain
+    implementation and against the sequence alone; with experts the captured steps equal the eager ones bit for
+    bit."""
+    cfg, _ = CONFIGS["dense"]
+    _, tensors = P.read_folder(folders["dense"])
+    lengths = [1 + (11 * i) % 60 for i in range(n)]
+    prompts = random_prompts(cfg["vocab_size"], lengths, seed=41)
+    feeds = random_prompts(cfg["vocab_size"], [5] * n, seed=42)
+    eng = tb.load(folders["dense"], dtype="bfloat16", max_tokens=128 * n, max_slots=n + 1)
+    together = _decode_batch(eng, prompts, feeds, 5)
+    assert n in eng._graphs, "the decode steps of this batch size should have been captured"
+    for i in range(0, n, 7):
+        alone = _decode_batch(eng, [prompts[i]], [feeds[i]], 5)
+        seq = prompts[i] + feeds[i]
+        ref = P.forward(cfg, tensors, seq, want=list(range(len(prompts[i]), len(seq))))
+        tol = BF16_REL_TOL * float(ref.abs().max())
+        for j in range(5):
+            assert float((together[j][i] - ref[j]).abs().max()) <= tol, f"sequence {i}, step {j}: against plain"
+            assert float((together[j][i] - alone[j][0]).abs().max()) <= 2 * tol, f"sequence {i}, step {j}: against alone"
+    cfgb, _ = CONFIGS["B"]
+    prompts = random_prompts(cfgb["vocab_size"], lengths, seed=43)
+    feeds = random_prompts(cfgb["vocab_size"], [5] * n, seed=44)
+    outs = []
+    for graphs in (True, False):
+        eng = tb.load(folders["B"], dtype="bfloat16", max_tokens=128 * n, max_slots=n + 1)
+        eng.use_graphs = graphs
+        outs.append(_decode_batch(eng, prompts, feeds, 5))
+        assert bool(eng._graphs) == graphs
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_batch_wider_than_the_graph_limit_runs_eagerly(dtype, folders):
+    cfg, _ = CONFIGS["A"]
+    prompts = random_prompts(cfg["vocab_size"], [3, 9, 1, 20, 5, 7], seed=51)
+    feeds = random_prompts(cfg["vocab_size"], [4] * 6, seed=52)
+    outs = []
+    for limit in (4, 256, 0):
+        eng = tb.load(folders["A"], dtype=dtype, max_tokens=1024)
+        eng.graph_max_batch = limit
+        six = _decode_batch(eng, prompts, feeds, 4)
+        four = _decode_batch(eng, prompts[:4], feeds[:4], 4)
+        assert (6 in eng._graphs) == (limit >= 6) and (4 in eng._graphs) == (limit >= 4)
+        outs.append(six + four)
+    for a, b, c in zip(*outs):
+        assert torch.equal(a, b) and torch.equal(a, c)

@@ -49,8 +49,11 @@ def _entry(rid, tokens, pos):
     return {"id": rid, "tokens": tokens, "want": list(range(len(tokens))), "_pos": pos}
 
 
-def _send(run, step, entries, end=()):
-    run.step(step, [{k: v for k, v in e.items() if not k.startswith("_")} for e in entries], end)
+def _send(run, step, entries, end=(), log=None):
+    clean = [{k: v for k, v in e.items() if not k.startswith("_")} for e in entries]
+    if log is not None:
+        log.append((step, clean, list(end)))
+    run.step(step, clean, end)
 
 
 def _verify(cfg, tensors, reqs, got, routes, dtype, label):
@@ -76,6 +79,7 @@ def test_replay_three_ways(name, dtype, folders, tmp_path):
     max_tokens = max(sum((len(prompts[i]) + 63) // 64 * 64 for i in b) for b in batches)
     run = TraceRun(folders[name], dtype, str(tmp_path / "out"), max_tokens)
     step = 0
+    sent = []      # the steps of (2) and (3), to be replayed once more through the CUDA-graph path
     try:
         # (1) each request alone and whole
         got, routes, reqs = {}, {}, {}
@@ -95,12 +99,12 @@ def test_replay_three_ways(name, dtype, folders, tmp_path):
             reqs[rid] = p
             cut = max(1, len(p) - 32)
             e = [_entry(rid, p[:cut], 0)]
-            _send(run, step, e, end=[rid] if cut == len(p) else [])
+            _send(run, step, e, end=[rid] if cut == len(p) else [], log=sent)
             _collect(run, step, cfg, e, got, routes)
             step += 1
             for j in range(cut, len(p)):
                 e = [_entry(rid, [p[j]], j)]
-                _send(run, step, e, end=[rid] if j == len(p) - 1 else [])
+                _send(run, step, e, end=[rid] if j == len(p) - 1 else [], log=sent)
                 _collect(run, step, cfg, e, got, routes)
                 step += 1
         _verify(cfg, tensors, reqs, got, routes, dtype, "last 32 one by one")
@@ -115,7 +119,7 @@ def test_replay_three_ways(name, dtype, folders, tmp_path):
                 reqs[ids[i]] = prompts[i]
             e = [_entry(ids[i], prompts[i][:len(prompts[i]) - ndec[i]], 0) for i in b]
             ended = [ids[i] for i in b if ndec[i] == 0]
-            _send(run, step, e, end=ended)
+            _send(run, step, e, end=ended, log=sent)
             _collect(run, step, cfg, e, got, routes)
             step += 1
             for s in range(max(ndec.values())):
@@ -123,12 +127,25 @@ def test_replay_three_ways(name, dtype, folders, tmp_path):
                 e = [_entry(ids[i], [prompts[i][len(prompts[i]) - ndec[i] + s]], len(prompts[i]) - ndec[i] + s)
                      for i in live]
                 ended = [ids[i] for i in live if s == ndec[i] - 1]
-                _send(run, step, e, end=ended)
+                _send(run, step, e, end=ended, log=sent)
                 _collect(run, step, cfg, e, got, routes)
                 step += 1
         _verify(cfg, tensors, reqs, got, routes, dtype, "unequal batches")
     finally:
         run.close()
+    # Recording the experts switches CUDA graphs off.  The same steps once more as generation runs them (decode
+    # steps replay a graph from their second use of a batch size on): the logits must not differ by a bit.
+    import numpy as np
+    again = TraceRun(folders[name], dtype, str(tmp_path / "graphs"), max_tokens, record_routing=False)
+    try:
+        for n, entries, end in sent:
+            again.step(n, entries, end)
+    finally:
+        again.close()
+    for n, entries, _ in sent:
+        a = np.fromfile(str(tmp_path / "out" / f"{n}.f32"), dtype="<f4")
+        b = np.fromfile(str(tmp_path / "graphs" / f"{n}.f32"), dtype="<f4")
+        assert a.shape == b.shape and np.array_equal(a, b), f"step {n}: the graph path gives other logits"
 
 
 def test_replay_rejects_overflow(folders, tmp_path):

@@ -6,7 +6,7 @@ experts and experts per token, feed-forward width, epsilon, rope base and pairin
 
 Weights are drawn with a standard deviation of 0.1 by default, not 0.02: at these widths 0.02
 gives attention scores near 1e-3, a flat softmax, and a model that would not notice a wrong mask
-or position.  The 0.02 workloads are run once as well (test_generate_gpu.py).
+or position.  The 0.02 workloads are run once as well (test_engine_gpu.py, test_published_workloads).
 """
 import json
 import os
@@ -52,6 +52,11 @@ FP32_TOL = 1e-4          # absolute, on logits of order one
 BF16_REL_TOL = 2.0 ** -6  # of the largest |logit| of the request
 
 
+def as_bfloat16(x):
+    """The rounding of the bfloat16 path where it stores an activation (``store=`` of the plain implementation)."""
+    return x.bfloat16().to(x.dtype)
+
+
 def make_folder(tmp, name, std=0.1, dtype="bfloat16"):
     import transformer_b200 as tb
     cfg, seed = CONFIGS[name]
@@ -77,7 +82,14 @@ def check_request(cfg, tensors, tokens, got_rows, routes, dtype, label="", store
     of the experts the engine chose.  Where the engine's set of experts differs from the plain
     implementation's free choice, the plain gap between the k-th and (k+1)-th router logit must be
     small against the rounding of the path (top-k is discontinuous; a near-tie may fall either way
-    and is then forced, not forgiven: a flip over a clear gap fails)."""
+    and is then forced, not forgiven: a flip over a clear gap fails).
+
+    The yardstick of the bfloat16 path is the plain implementation rounding to bfloat16 where the engine stores
+    an activation (sums, softmax, norms and the residual stream stay exact): it predicts what a bfloat16 path
+    computes up to the order of its sums, so it lies two to ten times closer to a right engine than the
+    unrounded one and a wrong engine stands out the more.  The rule itself is the same for both."""
+    if store is None and dtype == "bfloat16":
+        store = as_bfloat16
     forced = None
     if routes is not None and len(routes):
         forced = [[[int(e) for e in routes[l][a]] for a in range(len(tokens))] for l in range(len(routes))]
@@ -102,6 +114,65 @@ def check_request(cfg, tensors, tokens, got_rows, routes, dtype, label="", store
         worst = max(worst, diff)
         assert diff <= tol, f"{label}: position {pos} (first wrong of the request): |diff| {diff:.3e} > {tol:.3e}"
     return worst
+
+
+def check_generation(engine, cfg, tensors, prompts, tokens, batches, dtype, sample=None):
+    """Check what ``generate`` produced, through the engine's own step function and the plain implementation.
+
+    The batches are replayed teacher-forced on the generated tokens, step for step as generation ran them (prompts
+    together, then one token each), eagerly so that the chosen experts can be recorded.  The replayed logits are
+    the ones generation saw, bit for bit (same batch, same kernels; graphs equal eager steps), so:
+      * greedy: every generated token is exactly the argmax (lowest id on ties) of the replayed logits;
+      * sampled (``sample`` = (SampleArgs, {request: [u per token]})): the token is the one whose interval of the
+        distribution of the replayed logits holds u;
+      * the replayed logits equal the plain implementation's at every position, under the rule of the path, with the
+        routing-tie protocol of :func:`check_request`.
+    Every request must have generated the same number of tokens (no stop tokens)."""
+    rec = []
+    graphs, engine.use_graphs = engine.use_graphs, False
+    engine.recorder = lambda name, run, t: rec.append(t.cpu()) if name == "moe.topk_idx" else None
+    n_moe = n_moe_layers(cfg)
+    try:
+        for batch in batches:
+            n_new = len(tokens[batch[0]])
+            assert all(len(tokens[r]) == n_new for r in batch)
+            slots = [engine.open() for _ in batch]
+            rows = {r: {} for r in batch}
+            routes = {r: {} for r in batch}
+            for j in range(n_new):
+                feed = [list(prompts[r]) if j == 0 else [tokens[r][j - 1]] for r in batch]
+                lg = engine.step(slots, feed).cpu()
+                rt = torch.stack(rec) if n_moe else None           # [layers, tokens of the step, k]
+                rec.clear()
+                at = 0
+                for i, r in enumerate(batch):
+                    pos = len(prompts[r]) + j - 1
+                    rows[r][pos] = lg[i]
+                    for a in range(len(feed[i])):
+                        if rt is not None:
+                            routes[r][pos - len(feed[i]) + 1 + a] = rt[:, at + a, :]
+                    at += len(feed[i])
+                    tok = tokens[r][j]
+                    if sample is None or sample[0].greedy:
+                        assert tok == int(torch.argmax(lg[i])), f"request {r}, token {j}: {tok} is not the argmax"
+                    else:
+                        args, us = sample
+                        kept, probs = P.sample_distribution(lg[i], args.temperature, args.top_k, args.top_p)
+                        assert tok in kept, f"request {r}, token {j}: {tok} is outside the kept set"
+                        lo = sum(probs[:kept.index(tok)])
+                        assert lo - 1e-4 <= us[r][j] <= lo + probs[kept.index(tok)] + 1e-4, \
+                            f"request {r}, token {j}: u = {us[r][j]} misses the interval of {tok}"
+            for s in slots:
+                engine.close(s)
+            for r in batch:
+                seq = list(prompts[r]) + list(tokens[r][:-1])
+                rt = None
+                if n_moe:
+                    rt = torch.stack([routes[r][a] for a in range(len(seq))], dim=1).numpy()
+                check_request(cfg, tensors, seq, rows[r], rt, dtype, f"generation, request {r}")
+    finally:
+        engine.recorder = None
+        engine.use_graphs = graphs
 
 
 class TraceRun:
