@@ -20,6 +20,11 @@ pytestmark = pytest.mark.gpu
 
 
 class RunningSum(Mixer):
+    """All of the step's numbers come from the device arrays of ``ctx`` (slots, positions, which sequence a token
+    belongs to), never from the host lists, and nothing branches on a value: the forward pass can be captured into
+    a CUDA graph and replayed for other slots, which ``graph_safe`` declares."""
+    graph_safe = True
+
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
         self.d, self.decay = int(params["width"]), float(params["decay"])
@@ -32,9 +37,30 @@ class RunningSum(Mixer):
 
     def forward(self, ctx, x1, out, cache, state):
         assert cache is None and state is not None
+        seq, pos = ctx.tok_seq.long(), ctx.tok_pos.long()             # per token, on the device
+        slots = ctx.slots.long()                                      # per sequence
+        since = (pos - ctx.seq_pos0.long()[seq] + 1).double()         # tokens of its sequence up to and with this one
+        # s_i = decay^since_i * s_before + sum over earlier tokens m of the same sequence of decay^(pos_i - pos_m) x_m
+        same = (seq[:, None] == seq[None, :]) & (pos[:, None] >= pos[None, :])
+        # (a scalar base keeps torch.pow on the device: a tensor made from a Python number would be copied from
+        # the host, which a graph capture refuses)
+        weight = torch.pow(self.decay, (pos[:, None] - pos[None, :]).clamp(min=0).double()) * same
+        s = weight.float() @ x1.float() + torch.pow(self.decay, since).float()[:, None] * state[slots][seq]
+        last = ctx.seq_start.long()[1:] - 1                           # each sequence's last token of the step
+        state.index_copy_(0, slots, s[last])
+        out.copy_((s @ self.weights["w"].float().T).to(out.dtype))
+
+
+class RunningSumOnTheHost(RunningSum):
+    """The same mixer written the easy way: it walks the host lists.  A captured graph would replay it with the
+    slot numbers of the step that was captured, so it must not say ``graph_safe`` (the default is False), and the
+    engine then keeps the whole model on eager steps."""
+    graph_safe = False
+
+    def forward(self, ctx, x1, out, cache, state):
         w = self.weights["w"].float()
         lo = 0
-        for b, n in enumerate(ctx.h_lens):            # plain torch: a toy needs no kernel of its own
+        for b, n in enumerate(ctx.h_lens):
             s = state[ctx.h_slots[b]]
             for i in range(lo, lo + n):
                 s.mul_(self.decay).add_(x1[i].float())
@@ -79,6 +105,73 @@ def toy_registered():
     yield arch
     unregister_architecture("toy_running_sum")
     MIXERS.unregister("running_sum")
+
+
+def _decode(engine, prompts, feeds, slots_first=()):
+    """Open slots (after some that are only held to shift the numbering), prompts together, then one token each."""
+    held = [engine.open() for _ in slots_first]
+    slots = [engine.open() for _ in prompts]
+    engine.step(slots, prompts)
+    outs = [engine.step(slots, [[f[j]] for f in feeds]).cpu().clone() for j in range(len(feeds[0]))]
+    for s in slots + held:
+        engine.close(s)
+    return slots, outs
+
+
+def test_a_captured_batch_size_is_replayed_with_other_slots(toy_registered, tmp_path):
+    """The toy model says graph_safe, so its decode steps are captured.  The graph of batch size 2 is captured
+    with slots 0 and 1 and then replayed for sequences in slots 3 and 4 and in slots 1 and 0: the logits are those of
+    eager steps, bit for bit.  A part that read ``ctx.h_slots`` would have been replayed with slots 0 and 1."""
+    folder = tb.write_random_model(str(tmp_path / "toy"), CFG, seed=3, std=0.2)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 50, (n,), generator=g).tolist() for n in (7, 3)]
+    feeds = [torch.randint(0, 50, (6,), generator=g).tolist() for _ in range(2)]
+    eager = tb.load(folder, dtype="float32", max_tokens=512)
+    eager.use_graphs = False
+    _, want = _decode(eager, prompts, feeds)
+    engine = tb.load(folder, dtype="float32", max_tokens=512)
+    assert engine.graph_safe
+    slots, got = _decode(engine, prompts, feeds)
+    assert slots == [0, 1] and 2 in engine._graphs
+    graph = engine._graphs[2][0]
+    slots, moved = _decode(engine, prompts, feeds, slots_first=(0, 1, 2))
+    assert slots == [3, 4] and engine._graphs[2][0] is graph, "the same captured graph, other slots"
+    _, swapped = _decode(engine, prompts[::-1], feeds[::-1])
+    for a, b, c, d in zip(want, got, moved, swapped):
+        assert torch.equal(a, b) and torch.equal(a, c) and torch.equal(a, d.flip(0))
+
+
+def test_a_part_that_walks_host_lists_keeps_the_model_on_eager_steps(tmp_path):
+    MIXERS.register("running_sum", RunningSumOnTheHost)
+    register_architecture(Architecture("toy_running_sum", ToyConfig, toy_spec, lambda c: plan_from_spec(toy_spec(c))))
+    try:
+        folder = tb.write_random_model(str(tmp_path / "toy"), CFG, seed=3, std=0.2)
+        g = torch.Generator().manual_seed(4)
+        prompts = [torch.randint(0, 50, (n,), generator=g).tolist() for n in (7, 3)]
+        feeds = [torch.randint(0, 50, (6,), generator=g).tolist() for _ in range(2)]
+        engine = tb.load(folder, dtype="float32", max_tokens=512)
+        assert not engine.graph_safe and engine.use_graphs
+        _, first = _decode(engine, prompts, feeds)
+        _, moved = _decode(engine, prompts, feeds, slots_first=(0, 1, 2))
+        assert not engine._graphs, "nothing may be captured"
+        for a, b in zip(first, moved):
+            assert torch.equal(a, b)
+        out = tb.generate(engine, prompts, max_steps=4, stop_tokens=()).tokens      # device-fed steps, still eager
+        assert [len(t) for t in out] == [4, 4]
+    finally:
+        unregister_architecture("toy_running_sum")
+        MIXERS.unregister("running_sum")
+    # and the device form computes the same thing as the easy form
+    MIXERS.register("running_sum", RunningSum)
+    register_architecture(Architecture("toy_running_sum", ToyConfig, toy_spec, lambda c: plan_from_spec(toy_spec(c))))
+    try:
+        engine = tb.load(folder, dtype="float32", max_tokens=512)
+        _, device_form = _decode(engine, prompts, feeds)
+    finally:
+        unregister_architecture("toy_running_sum")
+        MIXERS.unregister("running_sum")
+    for a, b in zip(first, device_form):
+        assert float((a - b).abs().max()) <= 2e-4
 
 
 CFG = {"model_type": "toy_running_sum", "width": 40, "vocab": 50, "context": 96, "decay": 0.9}

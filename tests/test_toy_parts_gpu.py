@@ -5,8 +5,8 @@ rows, a position encoding -- defined HERE, registered, built and stepped without
     projection of the token;
   * "center_scale" (norm): y = (x - mean(x)) * w.  It sums a plain delta only, so the block must first add up the
     weighted rows that the mixture of experts before it left pending;
-  * "rope_scaled" (position): rotary angles of position / scale; the attention mixer asks any position part
-    for ``tables()`` and ``half_pairing`` and knows nothing else about it.
+  * "rope_scaled" (position): rotary angles of position / scale; the attention mixer asks a position part for
+    its ``rotation()`` (cos, sin, pairing) and knows nothing else about it.
 """
 import dataclasses
 
@@ -65,17 +65,16 @@ class RopeScaled(Position):
         super().__init__(params, dtype, device)
         self.dh, self.theta = int(params["dh"]), float(params["theta"])
         self.scale, self.positions = float(params["scale"]), int(params["positions"])
-        self.half_pairing = 0
         self._tables = None
 
-    def tables(self):
+    def rotation(self):
         if self._tables is None:
             i = torch.arange(self.dh // 2, dtype=torch.float64)
             ang = (torch.arange(self.positions, dtype=torch.float64) / self.scale)[:, None] * \
                 torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.dh)[None, :]
             self._tables = (torch.cos(ang).float().contiguous().to(self.device),
                             torch.sin(ang).float().contiguous().to(self.device))
-        return self._tables
+        return self._tables + (0,)
 
 
 @dataclasses.dataclass(frozen=True)

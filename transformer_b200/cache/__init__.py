@@ -1,2 +1,2 @@
-from .paged import Cache, CacheView
+from .paged import CACHE_KINDS, Cache, CacheStorage, CacheView
 from .slots import PAGE, CacheError, FreeList, SequenceTable

@@ -8,8 +8,11 @@ the free memory (models/llama/cuda/src/infer.rs:74-79).  Here one pool serves al
 * **pages** of 64 tokens; a sequence holds ceil(length / 64) of them, so the pool is sized by the
   most tokens that live sequences hold, each rounded up to 64;
 * **groups**: runs of the model whose mixers need the same kind of storage (kind, heads, head
-  size) share one pair of tensors K, V [runs, pages, nkvh, 64, dh]; another need gets a group of
-  its own.  Page numbers are common to the groups of kind "full";
+  size, the kind's own parameters) share one storage object; another need gets a group of its own.
+  The storage class is looked up by the need's ``kind`` in :data:`CACHE_KINDS`.  Kind "full" keeps
+  keys and values of every position in one pair of tensors K, V [runs, pages, nkvh, 64, dh]; page
+  numbers are common to the groups of kind "full".  Another kind (a window of the last W tokens, a
+  compressed cache) is a class registered under another name: see :class:`CacheStorage`;
 * **state**: for each run whose mixer asks for it, a tensor [slots, *shape], zeroed when a slot
   is opened.
 
@@ -22,8 +25,10 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts.base import CacheNeed, StateNeed
+from ..parts.base import CacheNeed, Registry, StateNeed
 from .slots import PAGE, CacheError, SequenceTable
+
+CACHE_KINDS = Registry("cache")     # CacheNeed.kind -> storage class
 
 
 @dataclass
@@ -35,13 +40,48 @@ class CacheView:
     kind: str = "full"
 
 
-class CacheGroup:
-    def __init__(self, need: CacheNeed, runs: List[int], n_pages: int, dtype, device):
+class CacheStorage:
+    """What a storage class must offer.  One object serves all runs with the same :class:`CacheNeed`.
+
+    ``__init__(need, runs, *, n_pages, max_slots, max_context, dtype, device)``: allocate for ``len(runs)`` runs;
+    ``n_pages`` pages of 64 tokens are what the cache's common page pool holds, ``max_slots`` the sequences that
+    can be live.  ``view(i, writable)``: what the i-th of these runs hands its mixer as ``cache`` (any object;
+    ``writable`` is False for a run that reads another run's cache).  ``open(slot)`` / ``close(slot)``: a
+    sequence starts or ends in this slot (storage addressed by slot, not by pages, puts itself in order here)."""
+
+    def __init__(self, need: CacheNeed, runs: List[int], *, n_pages: int, max_slots: int, max_context: int,
+                 dtype, device):
         self.need = need
         self.runs = runs
+
+    def view(self, index: int, writable: bool):
+        raise NotImplementedError
+
+    def open(self, slot: int) -> None:
+        pass
+
+    def close(self, slot: int) -> None:
+        pass
+
+    @property
+    def nbytes(self) -> int:
+        return 0
+
+
+@CACHE_KINDS.register("full")
+class CacheGroup(CacheStorage):
+    """Keys and values of every position, in the pages of the common pool."""
+
+    def __init__(self, need: CacheNeed, runs: List[int], *, n_pages: int, max_slots: int, max_context: int,
+                 dtype, device):
+        super().__init__(need, runs, n_pages=n_pages, max_slots=max_slots, max_context=max_context, dtype=dtype,
+                         device=device)
         shape = (len(runs), n_pages, need.nkvh, PAGE, need.dh)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
+
+    def view(self, index: int, writable: bool) -> CacheView:
+        return CacheView(self.k[index], self.v[index], writable=writable, kind=self.need.kind)
 
     @property
     def nbytes(self) -> int:
@@ -62,18 +102,21 @@ class Cache:
         self.table = SequenceTable(max_slots, n_pages, max_context)
         self.dtype = dtype
         self.device = device
-        self.groups: List[CacheGroup] = []
+        self.groups: List[CacheStorage] = []
         self._where: Dict[int, Tuple[int, int]] = {}     # run -> (group, index in group)
         self._reads_from = list(reads_from)
         by_need: Dict[CacheNeed, List[int]] = {}
         for r, need in enumerate(cache_needs):
             if need is None or reads_from[r] is not None:
                 continue
-            if need.kind != "full":
-                raise CacheError(f"cache kind {need.kind!r} has no storage class")
             by_need.setdefault(need, []).append(r)
         for need, runs in by_need.items():
-            g = CacheGroup(need, runs, n_pages, dtype, device)
+            try:
+                storage_cls = CACHE_KINDS.get(need.kind)
+            except ValueError as e:
+                raise CacheError(str(e)) from None
+            g = storage_cls(need, runs, n_pages=n_pages, max_slots=max_slots, max_context=max_context, dtype=dtype,
+                            device=device)
             for i, r in enumerate(runs):
                 self._where[r] = (len(self.groups), i)
             self.groups.append(g)
@@ -93,10 +136,14 @@ class Cache:
         slot = self.table.open()
         for t in self.state.values():
             t[slot].zero_()
+        for g in self.groups:
+            g.open(slot)
         return slot
 
     def close(self, slot: int) -> None:
         self.table.close(slot)
+        for g in self.groups:
+            g.close(slot)
 
     def extend(self, slot: int, new_tokens: int) -> int:
         return self.table.extend(slot, new_tokens)
@@ -117,8 +164,7 @@ class Cache:
         if owner not in self._where:
             return None
         g, i = self._where[owner]
-        grp = self.groups[g]
-        return CacheView(grp.k[i], grp.v[i], writable=(src is None), kind=grp.need.kind)
+        return self.groups[g].view(i, src is None)
 
     def state_of(self, run: int) -> Optional[torch.Tensor]:
         return self.state.get(run)

@@ -20,9 +20,8 @@ import torch
 from ..cache.paged import Cache
 from ..cache.slots import CacheError
 from ..csrc import lib
-from ..parts.block import Layer, resolve
-from ..parts.base import NORMS
-from ..parts.linear import matmul_nt
+from ..parts.block import build_layer, resolve
+from ..parts.base import EMBEDDINGS, HEADS, NORMS
 from ..parts.spec import ModelSpec
 from .context import StepContext, Workspace, weak_callback
 
@@ -44,8 +43,10 @@ class Engine:
         self.device = device
         self.max_step_tokens = int(max_step_tokens)
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
-        self.layers: List[Layer] = [Layer(ls, dtype, device) for ls in spec.layers]
+        self.embed = EMBEDDINGS.build(spec.embedding, dtype, device)
+        self.layers = [build_layer(ls, dtype, device) for ls in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, dtype, device)
+        self.head_part = HEADS.build(spec.head, dtype, device)
         self._bind(weights)
         runs = spec.order
         mixers = [self.layers[e.layer].mixer for e in runs]
@@ -61,7 +62,10 @@ class Engine:
         self._staging = []
         self._staging_next = 0
         self._staging_dev = None
-        # decode steps (one token per sequence) replay a CUDA graph captured per batch size
+        # decode steps (one token per sequence) replay a CUDA graph captured per batch size, if every part of the
+        # model says that its forward is fit for that (Part.graph_safe); one part that runs Python per step
+        # (reads host lists, branches on values) keeps the whole model on eager steps
+        self.graph_safe = all(p.graph_safe for p in [self.embed, self.final_norm, self.head_part, *self.layers])
         self.use_graphs = True
         self.graph_max_batch = 256
         self._graphs = {}        # batch size -> (graph, static logits)
@@ -69,16 +73,24 @@ class Engine:
 
     # ---- construction ---------------------------------------------------------------------
     def _bind(self, weights) -> None:
-        self.embedding = weights[("embedding", "table")]
-        self.head = weights[("head", "weight")]
-        V, d = self.spec.vocab, self.spec.width
-        for name, t in (("embedding", self.embedding), ("head", self.head)):
-            if tuple(t.shape) != (V, d):
-                raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {(V, d)}")
+        self.embed.bind({n: weights[("embedding", n)] for n in self.embed.parameters()})
+        self.head_part.bind({n: weights[("head", n)] for n in self.head_part.parameters()})
         for i, layer in enumerate(self.layers):
             for pname, part in layer.parts().items():
                 part.bind({n: weights[("layers", i, pname, n)] for n in part.parameters()})
         self.final_norm.bind({n: weights[("final_norm", n)] for n in self.final_norm.parameters()})
+
+    @property
+    def embedding(self) -> torch.Tensor:
+        """The embedding part's table (for a look at the weights; the engine itself goes through the part)."""
+        return self.embed.weights["table"]
+
+    @property
+    def head(self) -> torch.Tensor:
+        return self.head_part.weights["weight"]
+
+    def _graphs_on(self, B: int) -> bool:
+        return self.use_graphs and self.graph_safe and B <= self.graph_max_batch
 
     def _drop_graphs(self) -> None:
         """Captured graphs hold raw addresses of scratch and staging memory; when either moves, they go."""
@@ -185,7 +197,7 @@ class Engine:
         before = [self.cache.length(s) for s in slots]
         try:
             pos0 = [self.cache.extend(s, len(t)) for s, t in zip(slots, tokens)]
-            if one_each and (device_tokens is not None or (self.use_graphs and B <= self.graph_max_batch)):
+            if one_each and (device_tokens is not None or self._graphs_on(B)):
                 return self._run_decode(slots, tokens, pos0, device_tokens)
             if n_total <= self.max_step_tokens:
                 rows, base = [], 0
@@ -246,7 +258,7 @@ class Engine:
         ctx = StepContext(self, slots, tokens, pos0, list(range(B)), self._tile_sizes, fixed_pages=fixed)
         if device_tokens is not None:
             ctx.tok_ids.copy_(device_tokens.view(-1)[:B])
-        if not self.use_graphs or B > self.graph_max_batch:
+        if not self._graphs_on(B):
             return self._forward(ctx)
         entry = self._graphs.get(B)
         if entry is None:
@@ -289,9 +301,8 @@ class Engine:
 
     def _forward_on_stream(self, ctx: StepContext, logits_out=None) -> torch.Tensor:
         nt, d, V = ctx.nt, self.spec.width, self.spec.vocab
-        sfx = lib.suffix(self.dtype)
         x = ctx.scratch("stream", (nt, d), torch.float32)
-        lib.call("tb_embed_" + sfx, lib.ptr(ctx.tok_ids), lib.ptr(self.embedding), lib.ptr(x), nt, d)
+        self.embed.forward(ctx, x)
         pending = None
         for r, entry in enumerate(self.spec.order):
             layer = self.layers[entry.layer]
@@ -304,5 +315,5 @@ class Engine:
             xn = ctx.scratch("final.xn", (n_out, d), self.dtype)
             pending = resolve(pending, self.final_norm, ctx.scratch("block.delta", (nt, d), self.dtype))
             self.final_norm.forward(ctx, x, pending, ctx.want_rows, xn)
-            matmul_nt(xn, self.head, logits)
+            self.head_part.forward(ctx, xn, logits)
         return logits

@@ -44,11 +44,23 @@ class Attention(Mixer):
         self.tc_tile = lib.attention_tc_tile_tokens() if self.prompt_tile else 0
         self.tile_sizes = [self.general_tile] + ([self.prompt_tile, self.tc_tile] if self.prompt_tile else [])
 
+    @property
+    def graph_safe(self) -> bool:
+        return self.position is None or self.position.graph_safe
+
     def parameters(self):
-        return {
+        decl = {
             "wqkv": ParamDecl((self.qkv_width, self.d)),
             "wo": ParamDecl((self.d, self.nh * self.dh)),
         }
+        if self.position is not None:      # what the position encoding has learned travels with its mixer
+            decl.update({"position." + n: d for n, d in self.position.parameters().items()})
+        return decl
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.position is not None:
+            self.position.bind({n: tensors["position." + n] for n in self.position.parameters()})
 
     def cache_need(self):
         return CacheNeed("full", self.nkvh, self.dh)
@@ -59,10 +71,12 @@ class Attention(Mixer):
         qkv = ctx.scratch("attn.qkv", (nt, self.qkv_width), self.dtype)
         matmul_nt(x1, self.weights["wqkv"], qkv)
         table = ctx.page_table(cache)
-        if self.position is not None:
-            cos, sin = self.position.tables()
-            half = self.position.half_pairing
+        rotation = self.position.rotation() if self.position is not None else None
+        if rotation is not None:
+            cos, sin, half = rotation      # a rotary encoding: fused with the cache write below
         else:
+            if self.position is not None:
+                self.position.apply(ctx, qkv, self.nh, self.nkvh, self.dh)     # any other: by its own means
             cos, sin = ctx.identity_rotation(self.dh)
             half = 0
         kc, vc = (cache.k, cache.v) if cache.writable else (None, None)

@@ -7,20 +7,31 @@ talks to parts only through the methods below.
 ============  ===================================================================================
 kind          interface
 ============  ===================================================================================
+Embedding     ``forward(ctx, x)``: fill the float residual stream ``x`` [nt, d] for the step's tokens
+              (``ctx.tok_ids``, and ``ctx.tok_pos`` for an encoding that adds positions here).
 Norm          ``forward(ctx, x, delta, rows, y)``: ``v = x[rows] + delta[rows]`` (float sum; written
               back to ``x`` when ``rows`` is None), ``y = norm(v)``.  ``x`` is the float residual
               stream, ``delta`` the previous part's output or None.
 Mixer         ``forward(ctx, x1, out, cache, state)``: reads the normed activations ``x1`` [nt, d]
-              and writes its contribution to the stream into ``out`` [nt, d].  ``cache`` is the
-              run's :class:`~transformer_b200.cache.paged.CacheView` (None if ``cache_need()``
-              is None), ``state`` its per-sequence state tensor [slots, *shape] (None if
+              and writes its contribution to the stream into ``out`` [nt, d].  ``cache`` is what the
+              storage class of its ``cache_need().kind`` shows a run (None if ``cache_need()`` is
+              None), ``state`` its per-sequence state tensor [slots, *shape] (None if
               ``state_need()`` is None); rows of ``state`` are addressed by ``ctx.slots``.
 FeedForward   ``forward(ctx, x1, out)``; may return a ``WeightedRows`` instead of filling ``out``.
-Position      owned by the mixer that uses it; for rotary encodings ``tables()`` gives cos and sin.
+Position      owned by the mixer that uses it.  A rotary encoding answers ``rotation()`` with its
+              (cos, sin, half_pairing) and the mixer fuses the rotation with its cache write; any
+              other encoding answers None and is called as ``apply(ctx, qkv, nh, nkvh, dh)`` to
+              change the step's queries and keys in place by its own means.
+Head          ``forward(ctx, xn, logits)``: float logits [rows, vocab] of the normed rows ``xn``.
+Arrangement   how a layer's parts are put together in a block: built from a LayerSpec,
+              ``parts()`` (name -> part), ``mixer``, ``forward(ctx, x, pending, cache, state)``.
 ============  ===================================================================================
 
 All parts declare their parameters with :meth:`Part.parameters` (name -> shape, role, init) and
-receive the device tensors with :meth:`Part.bind`.
+receive the device tensors with :meth:`Part.bind`.  A part whose ``forward`` only launches work on the
+device that reads the step's numbers from ``ctx``'s DEVICE arrays (never from the ``h_*`` host lists,
+never a value copied back to the host) may set ``graph_safe = True``: decode steps of a model whose
+parts all say so are captured into CUDA graphs and replayed with new index arrays.
 """
 from __future__ import annotations
 
@@ -39,10 +50,17 @@ class ParamDecl:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Keys and values of every position ("full") for nkvh heads of size dh."""
+    """What a mixer wants kept for every sequence: ``kind`` names a registered storage class
+    (:data:`transformer_b200.cache.paged.CACHE_KINDS`; "full" = keys and values of every position in pages),
+    for nkvh heads of size dh; ``params`` holds what else the kind needs (a window's length, ...).  Runs with
+    equal needs share one storage object."""
     kind: str
     nkvh: int
     dh: int
+    params: Tuple[Tuple[str, Any], ...] = ()
+
+    def get(self) -> Dict[str, Any]:
+        return dict(self.params)
 
 
 @dataclass(frozen=True)
@@ -64,6 +82,8 @@ class WeightedRows:
 
 
 class Part:
+    graph_safe = False      # see the head of this file; the parts of this package set it
+
     def __init__(self, params: Dict[str, Any], dtype: torch.dtype, device: torch.device):
         self.params = dict(params)
         self.dtype = dtype
@@ -134,7 +154,25 @@ class FeedForward(Part):
 
 
 class Position(Part):
-    pass
+    def rotation(self):
+        """(cos, sin, half_pairing) of a rotary encoding -- float tables [positions, dh/2] on the device and 0
+        for adjacent pairs (2i, 2i+1), 1 for halves (i, i + dh/2) -- or None for any other encoding."""
+        return None
+
+    def apply(self, ctx, qkv, nh: int, nkvh: int, dh: int) -> None:
+        """For an encoding without ``rotation()``: change the step's queries and keys in place.  ``qkv`` is
+        [nt, (nh + 2 nkvh) dh] with the heads in the order q, k, v; ``ctx.tok_pos`` holds the positions."""
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, ctx, x) -> None:
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, ctx, xn, logits) -> None:
+        raise NotImplementedError
 
 
 class Registry:
@@ -153,17 +191,23 @@ class Registry:
     def unregister(self, kind: str) -> None:
         self._kinds.pop(kind, None)
 
-    def build(self, spec, dtype, device):
-        cls = self._kinds.get(spec.kind)
+    def get(self, kind: str):
+        cls = self._kinds.get(kind)
         if cls is None:
-            raise ValueError(f"unknown {self.what} kind {spec.kind!r}; registered: {sorted(self._kinds)}")
-        return cls(spec.get(), dtype, device)
+            raise ValueError(f"unknown {self.what} kind {kind!r}; registered: {sorted(self._kinds)}")
+        return cls
+
+    def build(self, spec, dtype, device):
+        return self.get(spec.kind)(spec.get(), dtype, device)
 
     def kinds(self):
         return sorted(self._kinds)
 
 
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
 NORMS = Registry("norm")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 POSITIONS = Registry("position encoding")
+ARRANGEMENTS = Registry("block arrangement")     # kind -> class(LayerSpec, dtype, device); see parts/block.py

@@ -21,6 +21,7 @@ ROUTER_TAIL_ROWS = 256      # up to this many tokens the norm before the experts
 class DenseSwiGLU(FeedForward):
     """params: width, di.  gate_up = x1 Wgu^T (gate rows first), h = silu(gate) * up, out = h Wd^T
     (compute.rs:278-292)."""
+    graph_safe = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -44,6 +45,7 @@ class MoE(FeedForward):
     router logits (float) -> the nexp_use largest, equal logits to the lower expert -> softmax over
     the kept logits (compute.rs:375-394) -> expert SwiGLU (compute.rs:320-328) -> weighted sum in
     descending-logit order, in float (compute.rs:329-330)."""
+    graph_safe = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)

@@ -9,6 +9,7 @@ from .base import NORMS, Norm, ParamDecl, WeightedRows
 class RMSNorm(Norm):
     """params: width, eps.  Statistics and the residual sum are float; one rounding at the store."""
 
+    graph_safe = True
     takes_weighted_rows = True
     can_warm = True
     tails = ("router",)

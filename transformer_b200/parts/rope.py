@@ -18,6 +18,7 @@ _TABLES = {}
 @POSITIONS.register("rope")
 class Rope(Position):
     """params: dh, theta, pairing ("adjacent" | "half"), positions (table length)."""
+    graph_safe = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -33,6 +34,10 @@ class Rope(Position):
     @property
     def half_pairing(self) -> int:
         return 1 if self.pairing == "half" else 0
+
+    def rotation(self):
+        cos, sin = self.tables()
+        return cos, sin, self.half_pairing
 
     def tables(self):
         key = (self.dh, self.theta, self.positions, str(self.device))

@@ -35,9 +35,10 @@ class PartSpec:
 class LayerSpec:
     mixer: PartSpec
     feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    arrangement: str = "pre_norm"   # x += mixer(norm(x)); x += ff(norm(x))  (compute.rs:204-336)
+    mixer_norm: Optional[PartSpec] = None          # an arrangement says which of these it needs
+    feed_forward_norm: Optional[PartSpec] = None
+    arrangement: str = "pre_norm"   # a registered kind; pre_norm: x += mixer(norm(x)); x += ff(norm(x))  (compute.rs:204-336)
+    extra: Tuple[Tuple[str, PartSpec], ...] = ()   # further parts by name, for arrangements that have them
 
 
 @dataclass(frozen=True)
