@@ -8,15 +8,19 @@ The default run has the layer sizes of the LLaMA-MoE-3.5B (4/16) shape (32 layer
 bfloat16 weights, a batch of 8 and prompt lengths uniform in [128, 2048].  A "step" is one decode
 step.  It prints ONE JSON line:
 
-  value      decoded tokens a second over K steps, timed on the device with CUDA events; the
-             sampled tokens stay on the device between steps
+  value      decoded tokens a second: regions of exactly K steps each, timed on the device with CUDA
+             events, repeated until at least a second has been timed; the median region counts
+             (ms_per_step, with the fastest and slowest region under "spread"); the sampled tokens
+             stay on the device between steps
   e2e        the same through transformer_b200.generate: host token lists in and out, the
              step's index arrays copied from pinned memory and the sampled tokens read back
              at every step
   prefill    one sequence of 2,048 tokens; frac = flops / time / the measured bf16 peak
   roofline   bytes the decode step has to read (every weight it uses once, the cache of the live
              requests) / its time, against the measured copy bandwidth
-  points     decode tokens a second at batch 1 and 64
+  points     decode tokens a second at batch 1 (a prompt of 1,088 tokens, the mean of the range) and
+             64, each with its mean context, distinct experts per layer, fraction of the copy
+             bandwidth and end-to-end figure
 
 Every timed step reads far more than the 126 MB of L2 (all weights), so no L2 flush is needed.
 """
@@ -41,6 +45,8 @@ SHAPE = {   # BASELINE.json configs[2]
 FULL_LAYERS = 32
 PROMPT_MIN, PROMPT_MAX = 128, 2048
 PREFILL_TOKENS = 2048
+MIN_TIMED_SECONDS = 1.0     # the K-step region is repeated until this much has been timed
+MAX_REGIONS = 40
 
 
 def peaks():
@@ -57,13 +63,15 @@ class Clocks:
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
+    def __init__(self, uuid=None):
+        """uuid: of the device the process runs on (cuda:0 of this process is rarely index 0 of a shared box)."""
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.proc = None
+        self.gpu = f"GPU-{uuid}" if uuid else "0"
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.QUERY}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
@@ -161,9 +169,13 @@ def main():
 
     batches = {B: lengths(B)}
     if not args.skip_points:
-        for b in (1, 64):
-            batches.setdefault(b, lengths(b))
-    room = max(sum((n + 2 * (K + W) + 8 + 63) // 64 * 64 for n in ls) for ls in batches.values())
+        batches.setdefault(1, [(PROMPT_MIN + PROMPT_MAX) // 2])     # one sequence: the mean of the range, not a draw
+        batches.setdefault(64, lengths(64))
+    # steps a run may take: warm-up and the regions (a second of them: some 500 steps of one sequence, 100 of 64)
+    def most_steps(b):
+        budget = max(K, 640 if b <= 16 else 160)
+        return min(W + 2 + min(MAX_REGIONS * K, budget), cfg["max_position_embeddings"] - PROMPT_MAX - 8)
+    room = max(sum((n + most_steps(len(ls)) + 8 + 63) // 64 * 64 for n in ls) for ls in batches.values())
     room = max(room, (PREFILL_TOKENS + 63) // 64 * 64)
     engine = tb.random_model(cfg, seed=0, dtype=args.dtype, max_tokens=room, max_slots=max(batches) + 1)
     sampler = Sampler(engine.device)
@@ -173,7 +185,7 @@ def main():
     # ---- prefill of 2,048 tokens ---------------------------------------------------------------
     ptoks = prompts_of([PREFILL_TOKENS])[0]
     times = []
-    for i in range(2 + 3):
+    for i in range(3 + 5):
         s = engine.open()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -182,9 +194,9 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         engine.close(s)
-        if i >= 2:
+        if i >= 3:
             times.append(e0.elapsed_time(e1))
-    p_ms = min(times)
+    p_ms = statistics.median(times)
     p_flops = prefill_flops(cfg, PREFILL_TOKENS)
     prefill = {"value": PREFILL_TOKENS / (p_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": p_ms,
                "frac": p_flops / (p_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
@@ -215,27 +227,40 @@ def main():
         for _ in range(W):
             one()
         torch.cuda.synchronize()
-        clk = Clocks()
+        uuid = getattr(torch.cuda.get_device_properties(dev), "uuid", None)
+        clk = Clocks(uuid)
         if with_clocks:
             clk.start()
             time.sleep(0.3)
         n0 = lib.launch_count
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(K):
-            one()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        launches = lib.launch_count - n0
+        regions, ctx_sum, steps_left = [], 0, most_steps(b) - W - 2
+        while (sum(regions) < MIN_TIMED_SECONDS * 1e3 or not regions) and len(regions) < MAX_REGIONS and steps_left >= K:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            before = sum(engine.cache.length(s) for s in slots)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(K):
+                one()
+            e1.record()
+            torch.cuda.synchronize()
+            regions.append(e0.elapsed_time(e1))
+            ctx_sum += before + b * (K // 2)          # the region's mean context
+            steps_left -= K
+        launches = (lib.launch_count - n0) // len(regions)
         clocks = clk.stop() if with_clocks else None
-        ctx_tokens = sum(engine.cache.length(s) for s in slots) - b * (K // 2)   # mean over the timed steps
+        ms = statistics.median(regions)
+        ctx_tokens = ctx_sum / len(regions)
         for s in slots:
             engine.close(s)
+        # end to end through the public entry point: the same prompts, K + 1 tokens each
+        res = tb.generate(engine, prompts, max_steps=W + 1, stop_tokens=())        # warm-up
+        res = tb.generate(engine, prompts, max_steps=K + 1, stop_tokens=())
         return {"tok_s": b * K / (ms * 1e-3), "ms_per_step": ms / K, "launches": launches, "clocks": clocks,
                 "bytes": decode_bytes(cfg, distinct, ctx_tokens, 2 if args.dtype == "bfloat16" else 4),
-                "distinct": sum(distinct) / max(1, len(distinct)), "ctx": ctx_tokens / b}
+                "distinct": sum(distinct) / max(1, len(distinct)), "ctx": ctx_tokens / b,
+                "spread": [min(regions) / K, max(regions) / K], "regions": len(regions),
+                "e2e": res.timing.decode_tokens / res.timing.decode_seconds,
+                "h2d": int(getattr(engine, "last_h2d_bytes", 0))}
 
     main_run = decode_run(batches[B], True)
     points = {}
@@ -244,20 +269,20 @@ def main():
             r = main_run if b == B else decode_run(batches[b], False)
             points[f"decode_b{b}"] = r["tok_s"]
             points[f"decode_b{b}_hbm_frac"] = r["bytes"] / (r["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"]
-
-    # ---- end to end through the public entry point --------------------------------------------
-    prompts = prompts_of(batches[B])
-    res = tb.generate(engine, prompts, max_steps=W + 1, stop_tokens=())        # warm-up
-    res = tb.generate(engine, prompts, max_steps=K + 1, stop_tokens=())
-    e2e_tok_s = res.timing.decode_tokens / res.timing.decode_seconds
-    h2d = int(getattr(engine, "last_h2d_bytes", 0))
+            points[f"decode_b{b}_ms"] = r["ms_per_step"]
+            points[f"decode_b{b}_mean_context"] = round(r["ctx"], 1)
+            points[f"decode_b{b}_distinct_experts"] = round(r["distinct"], 2)
+            points[f"decode_b{b}_e2e"] = r["e2e"]
+    e2e_tok_s, h2d = main_run["e2e"], main_run["h2d"]
 
     achieved = main_run["bytes"] / (main_run["ms_per_step"] * 1e-3) / 1e9
     out = {
         "metric": "decode tok/s at batch 8 (LLaMA-MoE-3.5B shape)", "value": main_run["tok_s"], "unit": "tokens/s",
         "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": main_run["ms_per_step"], "higher_is_better": True,
+        "spread": {"regions_of_k_steps": main_run["regions"], "ms_per_step_fastest": main_run["spread"][0],
+                   "ms_per_step_slowest": main_run["spread"][1]},
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
-        "data": "synthetic: random weights N(0, 0.02), uniform-random token ids", "impl": "ours",
+        "data": "synthetic: random weights ~N(0, 0.02) (counter-based, filled on the device), uniform-random token ids", "impl": "ours",
         "config": {
             "model": "llama-moe-3.5b-shape", "layers": args.layers, "layers_full": FULL_LAYERS, "width": 4096,
             "heads": 32, "kv_heads": 32, "head_dim": 128, "experts": 16, "experts_per_tok": 4, "expert_ffn": 688,
@@ -265,7 +290,7 @@ def main():
             "prompt_len_max": PROMPT_MAX, "mean_context": round(main_run["ctx"], 1), "seq_len": 1,
             "parallelism": "none", "l2": "every step reads all weights, far more than L2",
         },
-        "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
+        "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B + 4},
         "gpu_launches": main_run["launches"],
         "clocks": main_run["clocks"],
         "prefill": prefill,

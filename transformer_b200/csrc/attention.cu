@@ -20,3 +20,8 @@ int tb_attention_tile_tokens(int nh, int nkvh) {
 TB_ATTENTION(tb_attention_f32, float)
 TB_ATTENTION(tb_attention_bf16, __nv_bfloat16)
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_attention_f32)
+TB_TAPE_REGISTER(tb_attention_bf16)

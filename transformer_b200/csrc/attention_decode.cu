@@ -253,3 +253,8 @@ extern "C" {
 TB_ATT_DECODE(tb_attention_decode_f32, float)
 TB_ATT_DECODE(tb_attention_decode_bf16, __nv_bfloat16)
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_attention_decode_f32)
+TB_TAPE_REGISTER(tb_attention_decode_bf16)

@@ -316,3 +316,7 @@ extern "C" int tb_attention_decode_tma_bf16(const void* q, void* out, const void
     }
     return rc;
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_attention_decode_tma_bf16)

@@ -268,3 +268,7 @@ int tb_attention_prefill_bf16(const void* q, void* out, const void* kc, const vo
     return dh == 64 ? prefill_launch<64>(a, s) : prefill_launch<128>(a, s);
 }
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_attention_prefill_bf16)

@@ -377,3 +377,7 @@ int tb_attention_tc_bf16(const void* q, void* out, const void* kc, const void* v
     return dh == 64 ? attention_tc_launch<64>(mq, mk, mv, a, s) : attention_tc_launch<128>(mq, mk, mv, a, s);
 }
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_attention_tc_bf16)

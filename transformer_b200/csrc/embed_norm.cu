@@ -306,3 +306,12 @@ int tb_add_rmsnorm_router_bf16(float* x, const void* delta, const void* wy, cons
         RouterTail<__nv_bfloat16>{(const __nv_bfloat16*)router_w, E, route_k, route_idx, route_w});
 }
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_embed_f32)
+TB_TAPE_REGISTER(tb_embed_bf16)
+TB_TAPE_REGISTER(tb_add_rmsnorm_f32)
+TB_TAPE_REGISTER(tb_add_rmsnorm_bf16)
+TB_TAPE_REGISTER(tb_add_rmsnorm_router_f32)
+TB_TAPE_REGISTER(tb_add_rmsnorm_router_bf16)

@@ -168,3 +168,8 @@ extern "C" {
 TB_GEMM(tb_gemm_simt_f32, float)
 TB_GEMM(tb_gemm_simt_bf16, __nv_bfloat16)
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_gemm_simt_f32)
+TB_TAPE_REGISTER(tb_gemm_simt_bf16)

@@ -302,3 +302,7 @@ int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y
     return skinny_launch_nt<4>(a, out_kind, s);
 }
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_gemm_skinny_bf16)

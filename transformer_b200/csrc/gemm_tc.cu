@@ -538,3 +538,8 @@ int tb_gather_rows_bf16(const void* x, const int* rows, void* out, int M, int d,
     return tb_last_error();
 }
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_gemm_tc_bf16)
+TB_TAPE_REGISTER(tb_gather_rows_bf16)

@@ -42,6 +42,25 @@ _SIGNATURES: Dict[str, str] = {
     "tb_kernel_status_async": "p",
     "tb_random_fill_f32": "plulf", "tb_random_fill_bf16": "plulf",
 }
+class TapeArg(ctypes.Union):
+    _fields_ = [("p", ctypes.c_void_p), ("i", ctypes.c_int), ("f", ctypes.c_float), ("l", ctypes.c_longlong),
+                ("u", ctypes.c_ulonglong)]
+
+
+TAPE_MAX_ARGS = 24
+
+
+class TapeEntry(ctypes.Structure):
+    """One recorded launcher call (csrc/tape.h)."""
+    _fields_ = [("fn", ctypes.c_int), ("n_args", ctypes.c_int), ("ptr_mask", ctypes.c_uint), ("reserved", ctypes.c_int),
+                ("args", TapeArg * TAPE_MAX_ARGS)]
+
+
+class TapeMap(ctypes.Structure):
+    """Addresses [base, base + size) of the recorded layer move by delta for the layer being run."""
+    _fields_ = [("base", ctypes.c_ulonglong), ("size", ctypes.c_ulonglong), ("delta", ctypes.c_longlong)]
+
+
 _NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
 
@@ -72,6 +91,11 @@ def library() -> ctypes.CDLL:
                 fn = getattr(lib, name)
                 fn.argtypes = [_CODES[c] for c in codes]
                 fn.restype = _I
+            lib.tb_tape_index.argtypes = [ctypes.c_char_p]
+            lib.tb_tape_index.restype = _I
+            lib.tb_tape_replay.argtypes = [ctypes.POINTER(TapeEntry), _I, ctypes.POINTER(TapeMap), _I,
+                                           ctypes.POINTER(ctypes.c_int), _P]
+            lib.tb_tape_replay.restype = _I
             _lib = lib
     return _lib
 
@@ -114,6 +138,34 @@ def _stream() -> int:
     return _scope_stream if _scope_stream is not None else torch.cuda.current_stream().cuda_stream
 
 
+_recorder = None      # while a layer's calls are recorded: an object with launch(name, args) and foreign(kind, *tensors)
+
+
+class recording:
+    """``with recording(tape):`` every launcher call that succeeds inside is also reported to ``tape.launch(name,
+    args)``, and device work that does not go through a launcher reports itself with :func:`foreign`."""
+
+    def __init__(self, tape):
+        self.tape = tape
+
+    def __enter__(self):
+        global _recorder
+        self._before = _recorder
+        _recorder = self.tape
+        return self.tape
+
+    def __exit__(self, *exc):
+        global _recorder
+        _recorder = self._before
+        return False
+
+
+def foreign(kind: str, *tensors) -> None:
+    """Tell a recording that device work of another kind is about to run here (a library product, ...)."""
+    if _recorder is not None:
+        _recorder.foreign(kind, *tensors)
+
+
 def try_call(name: str, *args) -> bool:
     """Like :func:`call`, but a kernel that refuses the sizes (TB_ERR_UNSUPPORTED) answers False
     instead of raising, so the caller can take the general kernel."""
@@ -125,6 +177,8 @@ def try_call(name: str, *args) -> bool:
     if rc != 0:
         raise KernelError(f"{name}: {_error_text(rc)}")
     launch_count += 1
+    if _recorder is not None:
+        _recorder.launch(name, args)
     return True
 
 
@@ -136,6 +190,61 @@ def call(name: str, *args) -> None:
     rc = fn(*args, _stream())
     if rc != 0:
         raise KernelError(f"{name}: {_error_text(rc)}")
+    if _recorder is not None:
+        _recorder.launch(name, args)
+
+
+_tape_indices: Dict[str, int] = {}
+
+
+def tape_entries(calls) -> "ctypes.Array":
+    """[(launcher name, argument tuple)] as the array of TapeEntry that :func:`tape_replay` runs."""
+    arr = (TapeEntry * len(calls))()
+    for e, (name, args) in zip(arr, calls):
+        codes = _SIGNATURES[name]
+        if len(args) != len(codes) or len(args) > TAPE_MAX_ARGS:
+            raise KernelError(f"{name}: {len(args)} arguments recorded, {len(codes)} declared")
+        idx = _tape_indices.get(name)
+        if idx is None:
+            idx = library().tb_tape_index(name.encode())
+            if idx < 0:
+                raise KernelError(f"{name} is not registered for replay")
+            _tape_indices[name] = idx
+        e.fn, e.n_args, mask = idx, len(args), 0
+        for j, (c, v) in enumerate(zip(codes, args)):
+            if c == "p":
+                e.args[j].p = v or None
+                mask |= 1 << j
+            elif c == "i":
+                e.args[j].i = int(v)
+            elif c == "f":
+                e.args[j].f = float(v)
+            elif c == "l":
+                e.args[j].l = int(v)
+            else:
+                e.args[j].u = int(v)
+        e.ptr_mask = mask
+    return arr
+
+
+def tape_maps(moves) -> "ctypes.Array":
+    """[(base, size, delta)] as an array of TapeMap."""
+    arr = (TapeMap * max(1, len(moves)))()
+    for m, (base, size, delta) in zip(arr, moves):
+        m.base, m.size, m.delta = base, size, delta
+    return arr
+
+
+_failed_at = ctypes.c_int(0)
+
+
+def tape_replay(entries, maps, n_maps: int) -> None:
+    """Run recorded calls on torch's current stream with the pointers of ``maps`` moved."""
+    global launch_count
+    rc = library().tb_tape_replay(entries, len(entries), maps, n_maps, ctypes.byref(_failed_at), _stream())
+    if rc != 0:
+        raise KernelError(f"replayed call {_failed_at.value} of {len(entries)}: {_error_text(rc)}")
+    launch_count += len(entries)
 
 
 def ptr(t) -> int:

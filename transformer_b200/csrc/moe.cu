@@ -237,3 +237,12 @@ int tb_moe_combine_bf16(const void* y, const int* pair_row, const float* topk_w,
     return combine_launch<__nv_bfloat16>(y, pair_row, topk_w, delta, nt, d, k, s);
 }
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_router_f32)
+TB_TAPE_REGISTER(tb_router_bf16)
+TB_TAPE_REGISTER(tb_topk_softmax)
+TB_TAPE_REGISTER(tb_moe_dispatch)
+TB_TAPE_REGISTER(tb_moe_combine_f32)
+TB_TAPE_REGISTER(tb_moe_combine_bf16)

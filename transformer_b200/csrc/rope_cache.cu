@@ -190,3 +190,8 @@ int tb_rope_cache_bf16(void* qkv, const int* tok_seq, const int* tok_pos, const 
                                             nt, nh, nkvh, dh, half_pairing, s);
 }
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_rope_cache_f32)
+TB_TAPE_REGISTER(tb_rope_cache_bf16)

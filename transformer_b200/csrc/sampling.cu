@@ -279,3 +279,7 @@ extern "C" int tb_sample(const float* logits, long long ld, const float* u, int 
     TB_LAUNCH((sample_kernel), rows, SAMP_THREADS, 0, s, logits, ld, u, V, temperature, top_k, top_p, out_idx, out_val);
     return tb_last_error();
 }
+
+// replayable from C++ (tape.h)
+#include "tape.h"
+TB_TAPE_REGISTER(tb_sample)

@@ -152,11 +152,16 @@ class StepContext:
         event.record()
         self._dev = dev
         self._offsets = offsets
+        self._views: Dict[str, torch.Tensor] = {}       # made once per step: every layer asks for the same ones
+        self._scratch: Dict[tuple, torch.Tensor] = {}
         self.run_index = -1     # which entry of the run order is executing
 
     def _view(self, name: str) -> torch.Tensor:
-        o, n = self._offsets[name]
-        return self._dev[o:o + n]
+        v = self._views.get(name)
+        if v is None:
+            o, n = self._offsets[name]
+            v = self._views[name] = self._dev[o:o + n]
+        return v
 
     tok_ids = property(lambda self: self._view("tok_ids"))
     tok_seq = property(lambda self: self._view("tok_seq"))
@@ -178,7 +183,11 @@ class StepContext:
             rec(name, self.run_index, tensor.detach().clone())
 
     def scratch(self, name: str, shape, dtype, zero: bool = False) -> torch.Tensor:
-        return self.workspace.get(name, shape, dtype, zero)
+        key = (name, tuple(shape), dtype)
+        t = self._scratch.get(key)
+        if t is None:
+            t = self._scratch[key] = self.workspace.get(name, shape, dtype, zero)
+        return t
 
     def tiles(self, tq: int) -> AttentionTiles:
         """Each sequence's new tokens cut into tiles of tq tokens (the sizes the model's mixers

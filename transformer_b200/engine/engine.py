@@ -24,10 +24,22 @@ from ..parts.block import build_layer, resolve
 from ..parts.base import EMBEDDINGS, HEADS, NORMS
 from ..parts.spec import ModelSpec
 from .context import StepContext, Workspace, weak_callback
+from .tape import LayerTape, moves, run_tensors
 
 
 class StepError(ValueError):
     pass
+
+
+def _pending_signature(pending):
+    """What a block is handed by the block before it, as far as it shapes the block's launches: nothing, a tensor,
+    or weighted rows -- with the addresses, which are scratch memory and so the same from layer to layer."""
+    if pending is None:
+        return None
+    if isinstance(pending, torch.Tensor):
+        return ("t", pending.data_ptr(), tuple(pending.shape))
+    return ("w", pending.rows.data_ptr(), pending.index.data_ptr(), pending.weights.data_ptr(), pending.k,
+            tuple(pending.rows.shape))
 
 
 class Engine:
@@ -68,6 +80,17 @@ class Engine:
         self.graph_safe = all(p.graph_safe for p in [self.embed, self.final_norm, self.head_part, *self.layers])
         self.use_graphs = True
         self.graph_max_batch = 256
+        # layers of equal parts are recorded once per step and replayed from C++ for the other runs (engine/tape.py)
+        self.use_tapes = True
+        self._run_kind = []      # per run: a key that equal runs share, or None if the run cannot be replayed
+        self._run_tensors = []   # per run: its own tensors (weights, cache, state)
+        self._tape_maps = {}     # (recorded run, run) -> (TapeMap array, count)
+        for r, e in enumerate(runs):
+            layer = self.layers[e.layer]
+            tensors = run_tensors(layer, self.cache.view(r), self.cache.state_of(r)) \
+                if getattr(layer, "launches_only", False) else None
+            self._run_tensors.append(tensors)
+            self._run_kind.append(None if tensors is None else (spec.layers[e.layer], e.cache_of is None))
         self._graphs = {}        # batch size -> (graph, static logits)
         self._graph_seen = {}    # batch size -> decode steps run eagerly so far
 
@@ -295,6 +318,13 @@ class Engine:
         ctx = StepContext(self, slots, tokens, pos0, rows, self._tile_sizes, fixed_pages=fixed_pages)
         return self._forward(ctx, logits_out)
 
+    def _maps_between(self, r0: int, r: int):
+        key = (r0, r)
+        if key not in self._tape_maps:
+            mv = moves(self._run_tensors[r0], self._run_tensors[r])
+            self._tape_maps[key] = None if mv is None else (lib.tape_maps(mv), len(mv))
+        return self._tape_maps[key]
+
     def _forward(self, ctx: StepContext, logits_out=None) -> torch.Tensor:
         with lib.stream_scope():       # also inside a capture: the scope then holds the capturing stream
             return self._forward_on_stream(ctx, logits_out)
@@ -304,10 +334,32 @@ class Engine:
         x = ctx.scratch("stream", (nt, d), torch.float32)
         self.embed.forward(ctx, x)
         pending = None
+        taping = self.use_tapes and self.recorder is None
+        tapes = {}                  # kind of run and of what it is handed -> (recorded run, its tape)
         for r, entry in enumerate(self.spec.order):
             layer = self.layers[entry.layer]
             ctx.run_index = r
-            pending = layer.forward(ctx, x, pending, self.cache.view(r), self.cache.state_of(r))
+            kind = self._run_kind[r] if taping else None
+            if kind is None:
+                pending = layer.forward(ctx, x, pending, self.cache.view(r), self.cache.state_of(r))
+                continue
+            kind = (kind, _pending_signature(pending))
+            known = tapes.get(kind)
+            if known is None:
+                tape = LayerTape()
+                with lib.recording(tape):
+                    pending = layer.forward(ctx, x, pending, self.cache.view(r), self.cache.state_of(r))
+                tape.result = pending
+                tapes[kind] = (r, tape)
+                continue
+            r0, tape = known
+            if tape.usable and tape._segments is None:
+                tape.compile(self._run_tensors[r0])
+            maps = self._maps_between(r0, r) if tape.usable else None
+            if maps is None:
+                pending = layer.forward(ctx, x, pending, self.cache.view(r), self.cache.state_of(r))
+            else:
+                pending = tape.replay(maps[0], maps[1], self._run_tensors[r])
         n_out = len(ctx.h_want)
         logits = logits_out if logits_out is not None else \
             torch.empty((n_out, V), dtype=torch.float32, device=self.device)

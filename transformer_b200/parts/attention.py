@@ -48,6 +48,10 @@ class Attention(Mixer):
     def graph_safe(self) -> bool:
         return self.position is None or self.position.graph_safe
 
+    @property
+    def launches_only(self) -> bool:
+        return self.position is None or self.position.launches_only
+
     def parameters(self):
         decl = {
             "wqkv": ParamDecl((self.qkv_width, self.d)),

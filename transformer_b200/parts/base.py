@@ -83,6 +83,8 @@ class WeightedRows:
 
 class Part:
     graph_safe = False      # see the head of this file; the parts of this package set it
+    launches_only = False   # all device work goes through csrc.lib launchers (or reports itself with lib.foreign):
+                            # the engine may then record one layer's launches and replay them for its equals
 
     def __init__(self, params: Dict[str, Any], dtype: torch.dtype, device: torch.device):
         self.params = dict(params)

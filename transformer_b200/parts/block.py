@@ -42,6 +42,10 @@ class Layer:
     def graph_safe(self) -> bool:
         return all(p.graph_safe for p in self.parts().values())
 
+    @property
+    def launches_only(self) -> bool:
+        return all(p.launches_only for p in self.parts().values())
+
     def parts(self):
         return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
                 "feed_forward_norm": self.feed_forward_norm, "feed_forward": self.feed_forward}

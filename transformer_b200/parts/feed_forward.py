@@ -22,6 +22,7 @@ class DenseSwiGLU(FeedForward):
     """params: width, di.  gate_up = x1 Wgu^T (gate rows first), h = silu(gate) * up, out = h Wd^T
     (compute.rs:278-292)."""
     graph_safe = True
+    launches_only = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -46,6 +47,7 @@ class MoE(FeedForward):
     the kept logits (compute.rs:375-394) -> expert SwiGLU (compute.rs:320-328) -> weighted sum in
     descending-logit order, in float (compute.rs:329-330)."""
     graph_safe = True
+    launches_only = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)

@@ -82,6 +82,7 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w_is_weigh
     if to_float:
         gemm_simt(a, w, out, out_kind=1)
     else:
+        lib.foreign("mm", a, w, out)       # a recording repeats it with the other layers' own weight
         torch.mm(a, w.t(), out=out)
 
 

@@ -10,6 +10,7 @@ class RMSNorm(Norm):
     """params: width, eps.  Statistics and the residual sum are float; one rounding at the store."""
 
     graph_safe = True
+    launches_only = True
     takes_weighted_rows = True
     can_warm = True
     tails = ("router",)

@@ -19,6 +19,7 @@ _TABLES = {}
 class Rope(Position):
     """params: dh, theta, pairing ("adjacent" | "half"), positions (table length)."""
     graph_safe = True
+    launches_only = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
