@@ -112,3 +112,87 @@ def test_broken_files(tmp_path):
     open(str(tmp_path / "empty.gguf"), "wb").close()
     with pytest.raises(GGufError):
         GGufFile(str(tmp_path / "empty.gguf"))
+
+
+# ---- shards ------------------------------------------------------------------------------------------------------
+def write_raw_gguf(path, metadata, tensors):
+    """A GGUF file written by hand (version 3): metadata {key: ("u32" | "u16" | "f32" | "str", value)}, tensors
+    {name: torch tensor of float32 or bfloat16}.  The ``gguf`` package always adds general.architecture, which the
+    later shards of a model must not repeat."""
+    import struct
+
+    def s(x):
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+    kinds = {"u16": (2, "<H"), "u32": (4, "<I"), "f32": (6, "<f")}
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(metadata))
+    for k, (kind, v) in metadata.items():
+        head += s(k) + (struct.pack("<I", 8) + s(v) if kind == "str" else
+                        struct.pack("<I", kinds[kind][0]) + struct.pack(kinds[kind][1], v))
+    blobs, off = [], 0
+    for name, t in tensors.items():
+        raw = (t.view(torch.int16) if t.dtype == torch.bfloat16 else t).contiguous().numpy().tobytes()
+        head += s(name) + struct.pack("<I", t.dim()) + b"".join(struct.pack("<Q", d) for d in reversed(t.shape))
+        head += struct.pack("<IQ", 30 if t.dtype == torch.bfloat16 else 0, off)
+        blobs.append(raw + b"\0" * (-len(raw) % 32))
+        off += len(blobs[-1])
+    with open(path, "wb") as f:
+        f.write(head + b"\0" * (-len(head) % 32) + b"".join(blobs))
+    return path
+
+
+def _sharded(tmp_path, cfg, tensors, stem="model", count=3, extra_meta=None, repeat=None):
+    """The model cut into ``count`` shards: all metadata in the first, split.* keys in every one."""
+    m = LlamaMeta.from_dict(cfg)
+    meta = {"general.architecture": ("str", "llama"), "llama.block_count": ("u32", m.nblk),
+            "llama.embedding_length": ("u32", m.d), "llama.attention.head_count": ("u32", m.nh),
+            "llama.attention.head_count_kv": ("u32", m.nkvh), "llama.rope.dimension_count": ("u32", m.dh),
+            "llama.feed_forward_length": ("u32", m.di), "llama.expert_count": ("u32", m.nexp),
+            "llama.expert_used_count": ("u32", m.nexp_use), "llama.context_length": ("u32", m.nctx),
+            "llama.vocab_size": ("u32", m.nvoc), "llama.attention.layer_norm_rms_epsilon": ("f32", m.epsilon),
+            "llama.rope.freq_base": ("f32", m.theta), "rope_pairing": ("str", m.rope_pairing)}
+    names = list(tensors)
+    paths = []
+    for i in range(count):
+        part = {n: tensors[n] for n in names[i::count]}
+        if repeat and i == count - 1:
+            part[repeat] = tensors[repeat]
+        md = dict(meta) if i == 0 else {}
+        md.update({"split.no": ("u16", i), "split.count": ("u16", count), "general.alignment": ("u32", 32)})
+        if extra_meta and i == count - 1:
+            md.update(extra_meta)
+        paths.append(write_raw_gguf(str(tmp_path / f"{stem}-{i + 1:05d}-of-{count:05d}.gguf"), md, part))
+    return paths
+
+
+def test_a_sharded_model_loads_from_any_of_its_shards(tmp_path):
+    rules = tensor_plan(LlamaMeta.from_dict(TINY_A))
+    tensors = random_file_tensors(rules, 4, torch.bfloat16, std=0.1)
+    whole = load_weights(write_raw_gguf(str(tmp_path / "whole.gguf"), {}, tensors), rules, torch.float32, CPU)
+    paths = _sharded(tmp_path, TINY_A, tensors)
+    for p in (paths[0], paths[2]):
+        meta = LlamaMeta.from_dict(tb.read_config(p))
+        assert (meta.nblk, meta.nexp, meta.nvoc) == (2, 4, 256)
+        got = load_weights(p, tensor_plan(meta), torch.float32, CPU)
+        assert sorted(got) == sorted(whole) and all(torch.equal(got[k], whole[k]) for k in whole)
+
+
+def test_shard_faults_are_named(tmp_path):
+    from transformer_b200.weights.gguf import open_gguf, shard_paths
+    rules = tensor_plan(LlamaMeta.from_dict(TINY_A))
+    tensors = random_file_tensors(rules, 4, torch.bfloat16, std=0.1)
+    assert shard_paths("/x/m.gguf") == ["/x/m.gguf"] and shard_paths("/x/m-00001-of-00001.gguf") == ["/x/m-00001-of-00001.gguf"]
+    assert [p[-19:] for p in shard_paths("/x/m-00002-of-00003.gguf")] == [f"{i:05d}-of-00003.gguf" for i in (1, 2, 3)]
+    with pytest.raises(GGufError, match="outside 1..3"):
+        shard_paths("/x/m-00004-of-00003.gguf")
+    paths = _sharded(tmp_path, TINY_A, tensors, stem="gone")
+    import os
+    os.remove(paths[1])
+    with pytest.raises(GGufError, match="shards missing: gone-00002-of-00003.gguf"):
+        open_gguf(paths[0])
+    paths = _sharded(tmp_path, TINY_A, tensors, stem="twice", repeat="token_embd.weight")
+    with pytest.raises(GGufError, match="shard 3 .*tensor 'token_embd.weight' is in an earlier shard"):   # gguf/src/lib.rs:112-124
+        open_gguf(paths[1])
+    paths = _sharded(tmp_path, TINY_A, tensors, stem="key", extra_meta={"llama.block_count": ("u32", 2)})
+    with pytest.raises(GGufError, match="shard 3 .*metadata key 'llama.block_count' is in an earlier shard"):   # :99-110
+        open_gguf(paths[0])

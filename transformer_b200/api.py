@@ -29,8 +29,8 @@ def parse_dtype(dtype) -> torch.dtype:
 def read_config(folder: str) -> dict:
     """The configuration keys of a model: config.json of a folder, or the metadata of a .gguf file."""
     if os.path.isfile(folder) and folder.endswith(".gguf"):
-        from .weights.gguf import GGufFile
-        return GGufFile(folder).config()
+        from .weights.gguf import open_gguf
+        return open_gguf(folder).config()
     path = os.path.join(folder, "config.json")
     if not os.path.isfile(path):
         raise FileNotFoundError(f"{path} not found: a model folder holds config.json and model.safetensors")
@@ -46,7 +46,7 @@ def _typed(config):
 
 def load(folder: str, dtype="bfloat16", device: Union[str, torch.device] = "cuda:0", *,
          max_tokens: int = 8192, max_slots: Optional[int] = None, max_step_tokens: int = 8192) -> Engine:
-    """Engine for the model in ``folder`` (config.json + *.safetensors) or in one ``.gguf`` file; the
+    """Engine for the model in ``folder`` (config.json + *.safetensors) or in a ``.gguf`` file (any shard of a sharded one); the
     model class is chosen by the configuration.  ``dtype`` "bfloat16" is the serving path, "float32" the true 32-bit path."""
     dt = parse_dtype(dtype)
     dev = torch.device(device)

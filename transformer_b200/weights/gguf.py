@@ -2,9 +2,14 @@
 
 The reference reads nothing but GGUF (gguf/src/lib.rs:21-126): it maps the file, parses the key-value
 metadata and the tensor table, and hands out byte slices by tensor name.  This reader does the same
-for one file, for the value types the architecture's keys use and the tensor types the engine
-takes: F32, F16 and BF16.  Quantized tensor types are recognised by number and refused by the
-loader with their name.
+for the value types the architecture's keys use and the tensor types the engine takes: F32, F16
+and BF16.  Quantized tensor types are recognised by number and refused by the loader with their name.
+
+A model may be cut into shards ``<name>-0000N-of-0000M.gguf``: given the path of ANY shard,
+:func:`open_gguf` maps all M of them and merges their metadata and tensor tables, as the reference does
+(gguf/src/lib.rs:21-48 maps the shards, :76-126 merges them): ``general.alignment`` and ``split.*`` keys
+are every shard's own and are left out; any other metadata key, or a tensor name, that appears in two
+shards is an error.
 
 Layout (version 2 and 3, little endian):
     magic "GGUF" | version u32 | tensor count u64 | metadata count u64
@@ -15,8 +20,11 @@ Layout (version 2 and 3, little endian):
 from __future__ import annotations
 
 import mmap
+import os
+import re
 import struct
-from typing import Any, Dict, Tuple
+from concurrent.futures import ThreadPoolExecutor
+from typing import Any, Dict, List, Tuple
 
 import numpy as np
 import torch
@@ -134,17 +142,84 @@ class GGufFile:
         return out.view(torch.bfloat16) if tdt == torch.bfloat16 else out
 
     def config(self) -> dict:
-        """The metadata as a configuration dict: the architecture's own keys as they are, plus the
-        vocabulary size the way the reference finds it (the length of ``tokenizer.ggml.tokens``,
-        models/llama/common/src/storage.rs:48) or, failing that, the rows of ``token_embd.weight``."""
-        cfg = {k: v for k, v in self.metadata.items() if not isinstance(v, list) or len(v) <= 16}
-        arch = self.metadata.get("general.architecture")
-        if arch and f"{arch}.vocab_size" not in cfg:
-            toks = self.metadata.get("tokenizer.ggml.tokens")
-            if isinstance(toks, list):
-                cfg[f"{arch}.vocab_size"] = len(toks)
-            elif "token_embd.weight" in self.tensors:
-                cfg[f"{arch}.vocab_size"] = self.tensors["token_embd.weight"][0][0]
-        if "output.weight" not in self.tensors:
-            cfg.setdefault("tie_word_embeddings", True)                      # storage.rs:84
-        return cfg
+        return config_of(self.metadata, self.tensors)
+
+
+def config_of(metadata: Dict[str, Any], tensors: Dict[str, Tuple]) -> dict:
+    """The metadata as a configuration dict: the architecture's own keys as they are, plus the
+    vocabulary size the way the reference finds it (the length of ``tokenizer.ggml.tokens``,
+    models/llama/common/src/storage.rs:48) or, failing that, the rows of ``token_embd.weight``."""
+    cfg = {k: v for k, v in metadata.items() if not isinstance(v, list) or len(v) <= 16}
+    arch = metadata.get("general.architecture")
+    if arch and f"{arch}.vocab_size" not in cfg:
+        toks = metadata.get("tokenizer.ggml.tokens")
+        if isinstance(toks, list):
+            cfg[f"{arch}.vocab_size"] = len(toks)
+        elif "token_embd.weight" in tensors:
+            cfg[f"{arch}.vocab_size"] = tensors["token_embd.weight"][0][0]
+    if "output.weight" not in tensors:
+        cfg.setdefault("tie_word_embeddings", True)                      # storage.rs:84
+    return cfg
+
+
+_SHARD = re.compile(r"^(?P<stem>.*)-(?P<n>\d{5})-of-(?P<m>\d{5})\.gguf$")
+
+
+def shard_paths(path: str) -> List[str]:
+    """All shards of the model that ``path`` is one shard of, in order; [path] for a file that is whole."""
+    folder, name = os.path.split(path)
+    m = _SHARD.match(name)
+    if m is None or int(m["m"]) <= 1:
+        return [path]
+    count = int(m["m"])
+    if not (1 <= int(m["n"]) <= count):
+        raise GGufError(f"{name}: shard number {int(m['n'])} lies outside 1..{count}")
+    return [os.path.join(folder, f"{m['stem']}-{i:05d}-of-{count:05d}.gguf") for i in range(1, count + 1)]
+
+
+class GGufModel:
+    """A model from several shard files, behind the interface of :class:`GGufFile`."""
+
+    def __init__(self, paths: List[str]):
+        missing = [p for p in paths if not os.path.isfile(p)]
+        if missing:
+            raise GGufError(f"shards missing: {', '.join(os.path.basename(p) for p in missing)} "
+                            f"(of {len(paths)} in {os.path.dirname(paths[0]) or '.'})")
+        self.path = paths[0]
+        with ThreadPoolExecutor(max_workers=min(8, len(paths))) as pool:     # a thread per shard, gguf/src/lib.rs:82-96
+            self.shards = list(pool.map(GGufFile, paths))
+        self.metadata: Dict[str, Any] = {}
+        self.tensors: Dict[str, Tuple] = {}
+        self._where: Dict[str, GGufFile] = {}
+        for i, f in enumerate(self.shards):
+            for k, v in f.metadata.items():
+                if k == "general.alignment" or k.startswith("split."):
+                    continue                                                     # gguf/src/lib.rs:101-103
+                if k in self.metadata:
+                    raise GGufError(f"shard {i + 1} ({os.path.basename(f.path)}): metadata key {k!r} is in an earlier "
+                                    f"shard too")
+                self.metadata[k] = v
+            for name, info in f.tensors.items():
+                if name in self.tensors:
+                    raise GGufError(f"shard {i + 1} ({os.path.basename(f.path)}): tensor {name!r} is in an earlier "
+                                    f"shard too")
+                self.tensors[name] = info
+                self._where[name] = f
+
+    def names(self):
+        return self.tensors.keys()
+
+    def shape_dtype(self, name: str):
+        return self._where[name].shape_dtype(name)
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self._where[name].tensor(name)
+
+    def config(self) -> dict:
+        return config_of(self.metadata, self.tensors)
+
+
+def open_gguf(path: str):
+    """The model that ``path`` belongs to: one file, or all shards of a sharded one."""
+    paths = shard_paths(path)
+    return GGufFile(path) if len(paths) == 1 else GGufModel(paths)

@@ -123,10 +123,10 @@ def check_rules(rules: Sequence[TensorRule], present: Mapping[str, Tuple[Tuple[i
 
 
 def open_tensors(path: str):
-    """The tensors of a model: a folder or file of safetensors, or one GGUF file."""
+    """The tensors of a model: a folder or file of safetensors, or a GGUF file (any shard of a sharded one)."""
     if os.path.isfile(path) and path.endswith(".gguf"):
-        from .gguf import GGufFile
-        return GGufFile(path)
+        from .gguf import open_gguf
+        return open_gguf(path)
     return _Files(path)
 
 
