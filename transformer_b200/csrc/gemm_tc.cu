@@ -45,6 +45,7 @@
 #define TC_BN 256
 #define TC_BK 64
 #define TC_THREADS 192
+#define TC_SHARED_GROUPS 256                       // up to this many groups their offsets are kept in shared memory
 #define TC_MAX_STAGES 6
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_BHALF_BYTES (TC_BN / 2 * TC_BK * 2)     // half of the B tile: all that a block of a pair stages
@@ -77,7 +78,10 @@ struct TcTile {
     bool valid;
 };
 
-__device__ __forceinline__ TcTile tc_tile(const TcArgs& a, int t, int tiles_n, int n_out, int rows) {
+// `offsets`: the groups' row offsets, in shared memory when there are few enough groups (every role of the block
+// walks them for every tile: from global memory that is a chain of dependent loads, some 10 us for the last of 16
+// groups, on the way to the block's first copy).
+__device__ __forceinline__ TcTile tc_tile(const TcArgs& a, const int* offsets, int t, int tiles_n, int n_out, int rows) {
     TcTile r;
     const int tm = t / tiles_n;
     r.n0 = (t - tm * tiles_n) * n_out;
@@ -85,11 +89,11 @@ __device__ __forceinline__ TcTile tc_tile(const TcArgs& a, int t, int tiles_n, i
     r.row0 = tm * rows;
     r.row_end = a.M;
     r.valid = r.row0 < a.M;
-    if (a.group_offsets) {
+    if (offsets) {
         int cum = 0;
         r.valid = false;
         for (int g = 0; g < a.G; ++g) {
-            const int lo = a.group_offsets[g], hi = a.group_offsets[g + 1];
+            const int lo = offsets[g], hi = offsets[g + 1];
             const int tiles = (hi - lo + rows - 1) / rows;
             if (tm < cum + tiles) {
                 r.g = g;
@@ -114,6 +118,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     constexpr bool PAIR = CTAS == 2;
     __shared__ __align__(8) uint64_t bars[2 * TC_MAX_STAGES + 4];
     __shared__ uint32_t tmem_slot;
+    __shared__ int group_rows[TC_SHARED_GROUPS + 1];
+    const int* offsets = a.group_offsets;
+    if (a.group_offsets && a.G <= TC_SHARED_GROUPS) {
+        for (int i = threadIdx.x; i <= a.G; i += TC_THREADS) group_rows[i] = a.group_offsets[i];
+        offsets = group_rows;        // visible to all after the block-wide barrier below
+    }
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0;  // 0 leads the pair
@@ -160,7 +170,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             int s = 0;                        // its stage, and the parity of the stage's last use:
             uint32_t used = 1;                // kept as counters, since this one thread paces the whole block
             for (int t = pair; t < total && ok; t += pairs) {
-                const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
+                const TcTile tl = tc_tile(a, offsets, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
                 if (!tl.valid) continue;
                 const int a_row = tl.row0 + (int)rank * TC_BM;
                 const int b_row = tl.g * a.b_group_rows + tl.n0 + (int)rank * (a.dual ? a.N : a.n_tile / 2);
@@ -200,7 +210,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             int s = 0;                        // the stage of the next k-block and the parity of its use
             uint32_t use = 0;
             for (int t = pair; t < total && ok; t += pairs) {
-                const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
+                const TcTile tl = tc_tile(a, offsets, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
                 if (!tl.valid) continue;
                 const int buf = lt & 1;
                 if (lt >= 2) ok = mbar_wait(acc_empty(buf), ((lt >> 1) - 1) & 1, a.error, 5);   // drained two tiles ago
@@ -241,7 +251,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         bool ok = true;
         int lt = 0;
         for (int t = pair; t < total && ok; t += pairs) {
-            const TcTile tl = tc_tile(a, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
+            const TcTile tl = tc_tile(a, offsets, t, tiles_n, n_out, TcShape<CTAS>::ROWS);
             if (!tl.valid) continue;
             const int buf = lt & 1;
             const int m = tl.row0 + (int)rank * TC_BM + row, n0 = tl.n0;
@@ -249,14 +259,21 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             tc_fence_after();
             if (!ok) break;
             const uint32_t trow = tmem_base + buf * TC_BN + ((uint32_t)(quad * 32) << 16);
-            for (int c0 = 0; c0 < n_out; c0 += 32) {
+            // A warp whose 32 rows all lie beyond the group's rows has nothing to store (with a few rows per group
+            // that is most warps of most tiles): it skips the work and only hands the accumulator back.
+            const bool any_row = m - lane < tl.row_end;
+            for (int c0 = 0; any_row && c0 < n_out; c0 += 32) {
                 float v[32];
                 tmem_ld32(trow + c0, v);               // warp-collective: every lane takes part
                 if (a.dual) {
                     float u[32];
                     tmem_ld32(trow + a.n_tile / 2 + c0, u);
+                    // silu(g) * u = g * u / (1 + e^-g) in float, with the hardware's exponential and division
+                    // (2 ulp; the result is rounded to bfloat16 next).  The exact forms cost some hundred clocks
+                    // per value with only these four warps on the SM to hide them: measured, the epilogue of a tile
+                    // took 7 to 18 us, as long as streaming half of the tile's weights.
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                    for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i] * u[i], 1.0f + __expf(-v[i]));
                 }
                 if (wide) {
                     // A lane holds 32 columns of ONE row: stored from here, every instruction of the warp would touch

@@ -11,7 +11,8 @@ import torch
 
 from ..csrc import lib
 from .base import FEED_FORWARDS, FeedForward, NormTail, ParamDecl, WeightedRows
-from .linear import SKINNY_MAX_PAIRS, gemm_skinny, grouped_matmul, matmul_nt
+from . import linear
+from .linear import gemm_skinny, grouped_matmul, matmul_nt
 
 ROUTER_PRODUCT_ROWS = 256   # above this many tokens the router logits come from the prompt product kernel
 ROUTER_TAIL_ROWS = 256      # up to this many tokens the norm before the experts also routes
@@ -107,7 +108,7 @@ class MoE(FeedForward):
         nt = x1.shape[0]
         M = nt * self.k
         sfx = lib.suffix(self.dtype)
-        if self.dtype == torch.bfloat16 and M <= SKINNY_MAX_PAIRS and self.d % 8 == 0 and self.di % 8 == 0:
+        if self.dtype == torch.bfloat16 and M <= linear.SKINNY_MAX_PAIRS and self.d % 8 == 0 and self.di % 8 == 0:
             # a few tokens: no dispatch lists.  Row p = t * k + j of the experts' products is the pair (token t,
             # its j-th choice); every block of the product kernel finds its expert's pairs in the router's answer
             idx, w = (tail.index, tail.scores) if tail is not None else self.route(ctx, x1)[:2]

@@ -3,7 +3,7 @@
 float32: always the CUDA-core kernel of this package (plain FFMA: no reduced-precision matrix mode can slip in).
 bfloat16, by the number of rows:
   * up to 16 rows (decoding): ``gemm_skinny``, which streams the weights once through the tensor cores; the experts
-    of up to 128 (token, expert) pairs too, with the rows unsorted (``row_group``);
+    of up to 64 (token, expert) pairs too, with the rows unsorted (``row_group``);
   * more rows, one dense weight: the library (cuBLAS through ``torch.mm``), as the reference hands its ``mat_mul``
     to an operator library (compute.rs:425-455);
   * more rows, grouped (the experts of prompts and of wide decode batches) or float output (logits of many rows):
@@ -34,7 +34,8 @@ def gemm_simt(a, w, out, *, a_rows=None, group_offsets=None, groups=1, rows=None
 
 DENSE_TC = False           # dense bfloat16 products of many rows: this package's tcgen05 kernel instead of cuBLAS
 SKINNY_MAX_ROWS = 16       # dense: up to this many rows the weight-streaming kernel is used
-SKINNY_MAX_PAIRS = 128     # grouped: up to this many rows over all groups
+SKINNY_MAX_PAIRS = 64      # grouped: up to this many rows over all groups (measured in the decode step: the
+                           # tensor-core kernel wins from 96 (token, expert) pairs on, by 5 %; below, this one by 5..8 %)
 
 
 def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kind=0, max_group_rows=0,
