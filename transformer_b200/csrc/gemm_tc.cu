@@ -21,7 +21,10 @@
 //     shared memory per warp and leave as whole 128-byte lines (the product with the short K, the experts'
 //     down projection, was bound by its row-by-row stores: 68.6 -> 60.4 us at 16 x 512 rows, 0.88 -> 1.15
 //     PFLOP/s at 16 x 2,048);
-//   Warp roles: 0 = TMA producer, 1 = TMEM allocation (+ MMA issue in the leader), 2..5 = epilogue.
+//   Warp roles: 0 = TMA producer, 1 = TMEM allocation (+ MMA issue in the leader), 2..9 = epilogue: a warp reads the
+//   32 lanes of tensor memory its number allows (warp % 4), so two warps share each quarter of the rows and take
+//   alternate 64-column pieces.  (With four epilogue warps the product with the short K, 11 k-blocks a tile, was bound
+//   by its epilogue: the accumulator of a tile took as long to store as the next tile's products to compute.)
 //
 //   * grouped (the experts, models/llama/common/src/compute.rs:319-330 done as one product per
 //     expert over all of its tokens): rows of A are sorted by group; B is the stack of the groups'
@@ -44,7 +47,8 @@
 #define TC_BM 128                                  // rows of a tile per block; a pair covers 2 * TC_BM
 #define TC_BN 256
 #define TC_BK 64
-#define TC_THREADS 192
+#define TC_THREADS 320
+#define TC_EPI_WARPS 8                             // two per quarter of the tensor memory's lanes
 #define TC_SHARED_GROUPS 256                       // up to this many groups their offsets are kept in shared memory
 #define TC_MAX_STAGES 6
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
@@ -148,7 +152,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(acc_full(i), 1);
-            mbar_init(acc_empty(i), 4 * CTAS);    // the leader's: one arrival per epilogue warp of every block
+            mbar_init(acc_empty(i), TC_EPI_WARPS * CTAS);    // the leader's: one arrival per epilogue warp of every block
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -242,8 +246,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5 of both blocks, TMEM lanes 32 * (warp % 4) ----------------
+        // ---------------- epilogue: warps 2..9 of both blocks, TMEM lanes 32 * (warp % 4) ----------------
         const int quad = warp & 3;
+        const int piece = (warp - 2) >> 2;      // which of the alternate 64-column pieces this warp takes
         const int row = quad * 32 + lane;
         // bfloat16 results whose rows start on 16-byte boundaries leave through this warp's strip of shared memory
         uint8_t* strip = smem_raw + (smem_base - smem_u32(smem_raw)) + TC_STAGES * TC_STAGE_BYTES + (warp - 2) * TC_STRIP_BYTES;
@@ -263,6 +268,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             // that is most warps of most tiles): it skips the work and only hands the accumulator back.
             const bool any_row = m - lane < tl.row_end;
             for (int c0 = 0; any_row && c0 < n_out; c0 += 32) {
+                if (((c0 >> 6) & 1) != piece) continue;
                 float v[32];
                 tmem_ld32(trow + c0, v);               // warp-collective: every lane takes part
                 if (a.dual) {
@@ -418,7 +424,7 @@ int* tc_error_ptr() {
 
 template <int CTAS>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, cudaStream_t s) {
-    const size_t smem = (size_t)TcShape<CTAS>::STAGES * TcShape<CTAS>::STAGE_BYTES + 4 * TC_STRIP_BYTES + 1024;
+    const size_t smem = (size_t)TcShape<CTAS>::STAGES * TcShape<CTAS>::STAGE_BYTES + TC_EPI_WARPS * TC_STRIP_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
