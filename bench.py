@@ -45,6 +45,20 @@ SHAPE = {   # BASELINE.json configs[2]
 FULL_LAYERS = 32
 PROMPT_MIN, PROMPT_MAX = 128, 2048
 PREFILL_TOKENS = 2048
+# The other shapes BASELINE.json names (configs[3], configs[4]); not the default and not the headline: further sizes
+# for the same kernels.  name -> (config, layers of the full model, prompt length range)
+OTHER_SHAPES = {
+    "mixtral-8x7b": ({
+        "model_type": "llama", "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "num_local_experts": 8,
+        "num_experts_per_tok": 2, "max_position_embeddings": 32768, "vocab_size": 32000, "rms_norm_eps": 1e-5,
+        "rope_theta": 1e6, "tie_word_embeddings": False}, 32, (512, 8192)),
+    "mixtral-8x22b": ({
+        "model_type": "llama", "num_hidden_layers": 16, "hidden_size": 6144, "num_attention_heads": 48,
+        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 16384, "num_local_experts": 8,
+        "num_experts_per_tok": 2, "max_position_embeddings": 65536, "vocab_size": 32768, "rms_norm_eps": 1e-5,
+        "rope_theta": 1e6, "tie_word_embeddings": False}, 56, (1, 16384)),
+}
 MIN_TIMED_SECONDS = 1.0     # the K-step region is repeated until this much has been timed
 MAX_REGIONS = 40
 
@@ -129,6 +143,7 @@ def decode_bytes(c, distinct_experts_per_layer, context_tokens, elem=2):
 
 
 def main():
+    global PROMPT_MIN, PROMPT_MAX, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -138,6 +153,10 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points")
+    ap.add_argument("--shape", default="llama-moe-3.5b", choices=["llama-moe-3.5b", *OTHER_SHAPES],
+                    help="layer sizes: the benchmark's (default) or another shape BASELINE.json names")
+    ap.add_argument("--prompt-max", type=int, default=0, help="longest prompt drawn (default: the shape's own)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -157,7 +176,15 @@ def main():
     from transformer_b200.sampling import Sampler
 
     pk = peaks()
-    cfg = dict(SHAPE, num_hidden_layers=args.layers)
+    shape, full_layers = SHAPE, FULL_LAYERS
+    if args.shape != "llama-moe-3.5b":
+        shape, full_layers, (PROMPT_MIN, PROMPT_MAX) = OTHER_SHAPES[args.shape]
+        if args.layers == FULL_LAYERS:
+            args.layers = shape["num_hidden_layers"]
+    if args.prompt_max:
+        PROMPT_MAX = max(PROMPT_MIN, args.prompt_max)
+    PREFILL_TOKENS = args.prefill_tokens
+    cfg = dict(shape, num_hidden_layers=args.layers)
     K, W, B = args.steps, args.warmup, args.batch
     gen = torch.Generator().manual_seed(1234)
 
@@ -277,16 +304,19 @@ def main():
 
     achieved = main_run["bytes"] / (main_run["ms_per_step"] * 1e-3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (LLaMA-MoE-3.5B shape)", "value": main_run["tok_s"], "unit": "tokens/s",
+        "metric": f"decode tok/s at batch {B} ({'LLaMA-MoE-3.5B' if args.shape == 'llama-moe-3.5b' else args.shape} shape)",
+        "value": main_run["tok_s"], "unit": "tokens/s",
         "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": main_run["ms_per_step"], "higher_is_better": True,
         "spread": {"regions_of_k_steps": main_run["regions"], "ms_per_step_fastest": main_run["spread"][0],
                    "ms_per_step_slowest": main_run["spread"][1]},
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic: random weights ~N(0, 0.02) (counter-based, filled on the device), uniform-random token ids", "impl": "ours",
         "config": {
-            "model": "llama-moe-3.5b-shape", "layers": args.layers, "layers_full": FULL_LAYERS, "width": 4096,
-            "heads": 32, "kv_heads": 32, "head_dim": 128, "experts": 16, "experts_per_tok": 4, "expert_ffn": 688,
-            "vocab": 32000, "context": 4096, "global_batch": B, "prompt_len_min": PROMPT_MIN,
+            "model": args.shape + "-shape", "layers": args.layers, "layers_full": full_layers,
+            "width": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "experts": cfg["num_local_experts"],
+            "experts_per_tok": cfg["num_experts_per_tok"], "expert_ffn": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "context": cfg["max_position_embeddings"], "global_batch": B, "prompt_len_min": PROMPT_MIN,
             "prompt_len_max": PROMPT_MAX, "mean_context": round(main_run["ctx"], 1), "seq_len": 1,
             "parallelism": "none", "l2": "every step reads all weights, far more than L2",
         },

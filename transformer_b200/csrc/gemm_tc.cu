@@ -74,9 +74,9 @@ struct TcArgs {
 };
 
 // ---- the kernel ----------------------------------------------------------------------------
-// Persistent: a block (or pair) walks the tiles  unit, unit + units, ...  (column tiles of one row tile are
-// neighbours in that order, so concurrent units share its A tile in L2).  The TMA ring runs on across tile
-// boundaries.
+// Persistent: a block (or pair) walks the tiles  unit, unit + units, ...  in the order tc_tile gives them (one
+// matrix: column tiles of one row tile are neighbours, so concurrent units share its A tile in L2; groups: see
+// there).  The TMA ring runs on across tile boundaries.
 struct TcTile {
     int g, row0, row_end, n0;
     bool valid;
@@ -87,27 +87,40 @@ struct TcTile {
 // groups, on the way to the block's first copy).
 __device__ __forceinline__ TcTile tc_tile(const TcArgs& a, const int* offsets, int t, int tiles_n, int n_out, int rows) {
     TcTile r;
-    const int tm = t / tiles_n;
-    r.n0 = (t - tm * tiles_n) * n_out;
+    if (!offsets) {
+        const int tm = t / tiles_n;
+        r.n0 = (t - tm * tiles_n) * n_out;
+        r.g = 0;
+        r.row0 = tm * rows;
+        r.row_end = a.M;
+        r.valid = r.row0 < a.M;
+        return r;
+    }
+    // Groups: the tiles of a group are numbered column tile by column tile, the group's row tiles innermost.  Blocks
+    // that run at the same time take consecutive numbers, so the few row tiles of a group that need the SAME tile
+    // of its weights fetch it together (once from memory, the others from L2), and what they do not share, the
+    // group's rows of A, is a few megabytes that stay in L2.  With the row tiles outermost every weight came from
+    // memory once per row tile whenever a group's weights exceed L2 (experts 14,336 wide: 235 MB per group,
+    // four row tiles: four times the traffic, and the product was bound by it).
+    r.valid = false;
     r.g = 0;
-    r.row0 = tm * rows;
-    r.row_end = a.M;
-    r.valid = r.row0 < a.M;
-    if (offsets) {
-        int cum = 0;
-        r.valid = false;
-        for (int g = 0; g < a.G; ++g) {
-            const int lo = offsets[g], hi = offsets[g + 1];
-            const int tiles = (hi - lo + rows - 1) / rows;
-            if (tm < cum + tiles) {
-                r.g = g;
-                r.row0 = lo + (tm - cum) * rows;
-                r.row_end = hi;
-                r.valid = true;
-                break;
-            }
-            cum += tiles;
+    r.row0 = r.row_end = r.n0 = 0;
+    int cum = 0;
+    for (int g = 0; g < a.G; ++g) {
+        const int lo = offsets[g], hi = offsets[g + 1];
+        const int tiles_r = (hi - lo + rows - 1) / rows;
+        const int n = tiles_r * tiles_n;
+        if (t < cum + n) {
+            const int local = t - cum;
+            const int tn = local / tiles_r, tr = local - tn * tiles_r;
+            r.g = g;
+            r.row0 = lo + tr * rows;
+            r.row_end = hi;
+            r.n0 = tn * n_out;
+            r.valid = true;
+            break;
         }
+        cum += n;
     }
     return r;
 }
