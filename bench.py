@@ -12,9 +12,9 @@ step.  It prints ONE JSON line:
              events, repeated until at least a second has been timed; the median region counts
              (ms_per_step, with the fastest and slowest region under "spread"); the sampled tokens
              stay on the device between steps
-  e2e        the same through transformer_b200.generate: host token lists in and out, the
-             step's index arrays copied from pinned memory and the sampled tokens read back
-             at every step
+  e2e        the same through transformer_b200.generate (as many steps as all regions together): host
+             token lists in and out, the step's index arrays copied from pinned memory and the
+             sampled tokens read back at every step
   prefill    one sequence of 2,048 tokens; frac = flops / time / the measured bf16 peak
   roofline   bytes the decode step has to read (every weight it uses once, the cache of the live
              requests) / its time, against the measured copy bandwidth
@@ -279,9 +279,10 @@ def main():
         ctx_tokens = ctx_sum / len(regions)
         for s in slots:
             engine.close(s)
-        # end to end through the public entry point: the same prompts, K + 1 tokens each
+        # end to end through the public entry point: the same prompts, and as many decode steps as the device-timed
+        # regions had in all (K of them would be a tenth of a second, mostly the clocks' recovery from the prompts)
         res = tb.generate(engine, prompts, max_steps=W + 1, stop_tokens=())        # warm-up
-        res = tb.generate(engine, prompts, max_steps=K + 1, stop_tokens=())
+        res = tb.generate(engine, prompts, max_steps=K * len(regions) + 1, stop_tokens=())
         return {"tok_s": b * K / (ms * 1e-3), "ms_per_step": ms / K, "launches": launches, "clocks": clocks,
                 "bytes": decode_bytes(cfg, distinct, ctx_tokens, 2 if args.dtype == "bfloat16" else 4),
                 "distinct": sum(distinct) / max(1, len(distinct)), "ctx": ctx_tokens / b,
