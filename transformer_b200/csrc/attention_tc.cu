@@ -9,10 +9,12 @@
 //   warp 0   TMA: the Q tile once, then K and V of each page into a two-stage ring (the cache of a
 //            layer is one 2-D tensor [pages * nkvh * 64, dh], so a page of a head is a box of rows)
 //   warp 1   one thread issues  S = Q K^T  (128 x 64, accumulator S in TMEM) and  O += P V
-//            (128 x dh, accumulator O in TMEM; V is the MN-major B operand, straight as cached)
+//            (128 x dh, accumulator O in TMEM; P from TMEM, V is the MN-major B operand, straight as cached)
 //   warps 2-5  128 threads = the 128 query rows: read their row of S from TMEM, mask, running
-//            maximum and sum, P = exp2(s - m) rounded to bfloat16 into shared memory (swizzled as
-//            the A operand wants it), and at the end O / l to memory.
+//            maximum and sum, P = exp2(s - m) rounded to bfloat16 and written back into tensor memory
+//            where the row of S was (tcgen05.st): the second product takes its A operand from there
+//            (tcgen05.mma with A in tensor memory), so P never passes through shared memory; and at
+//            the end O / l to memory.
 //
 // The running maximum is only raised when it grows by more than 8 (in the exponent's log2 units):
 // then the row of O in TMEM is rescaled; otherwise P is simply computed against the older maximum
@@ -73,6 +75,20 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 32 consecutive 32-bit columns of this thread's lane, as they are (packed bfloat16 pairs)
+__device__ __forceinline__ void tmem_st32_words(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 template <int DH>
 __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                  const __grid_constant__ CUtensorMap map_k,
@@ -80,7 +96,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                                                                  const AtArgs a) {
     pdl_sync();
     constexpr int KB = DH / 64;                          // 64-wide column boxes of a row of dh values
-    constexpr uint32_t Q_BYTES = AT_BM * DH * 2, KV_BYTES = AT_BN * DH * 2, P_BYTES = AT_BM * AT_BN * 2;
+    constexpr uint32_t Q_BYTES = AT_BM * DH * 2, KV_BYTES = AT_BN * DH * 2;
     constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;
     constexpr uint32_t TMEM_COLS = 256;                  // S twice (2 x 64 columns) and O (dh columns)
     // All shared memory is dynamic and the kernel has no static shared memory, so the tiles start at the
@@ -88,9 +104,9 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
     // on an SM.  The barriers and the TMEM slot follow the tiles.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
-    const uint32_t sq = smem_base, sp = sq + Q_BYTES, skv = sp + P_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + Q_BYTES + P_BYTES + AT_STAGES * STAGE_BYTES);   // 4 * stages + 5
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 4 * AT_STAGES + 5);
+    const uint32_t sq = smem_base, skv = sq + Q_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + Q_BYTES + AT_STAGES * STAGE_BYTES);   // 4 * stages + 7
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 4 * AT_STAGES + 7);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (smem_base & 1023u) {                              // never expected; refuse rather than compute garbage
         if (threadIdx.x == 0) atomicCAS(a.error, 0, 19);
@@ -113,8 +129,11 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
     auto k_empty = [&](int s) { return bar0 + 8u * (AT_STAGES + s); };
     auto v_full = [&](int s) { return bar0 + 8u * (2 * AT_STAGES + s); };
     auto v_empty = [&](int s) { return bar0 + 8u * (3 * AT_STAGES + s); };
-    const uint32_t q_full = bar0 + 8u * (4 * AT_STAGES), p_ready = q_full + 8, o_done = q_full + 16;
+    const uint32_t q_full = bar0 + 8u * (4 * AT_STAGES), o_done = q_full + 16;
     auto s_full = [&](int i) { return q_full + 24 + 8u * i; };      // one per S buffer
+    // ... and one per S buffer for "P is in it": a softmax warp may be a tile ahead of the others (nothing holds it
+    // back but the scores), and its arrival for the next tile must not count towards this one
+    auto p_ready = [&](int i) { return i == 0 ? q_full + 8 : q_full + 40; };
     if (threadIdx.x == 0) {
         for (int s = 0; s < AT_STAGES; ++s) {
             mbar_init(k_full(s), 1);
@@ -125,7 +144,8 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
         mbar_init(q_full, 1);
         mbar_init(s_full(0), 1);
         mbar_init(s_full(1), 1);
-        mbar_init(p_ready, 4);       // one arrival per softmax warp
+        mbar_init(p_ready(0), 4);    // one arrival per softmax warp
+        mbar_init(p_ready(1), 4);
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -200,7 +220,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                ok = mbar_wait(p_ready, j & 1, a.error, 13);       // P is in shared memory (and S of tile j has been read)
+                ok = mbar_wait(p_ready(j & 1), (j >> 1) & 1, a.error, 13);   // P is in tensor memory, where S of tile j was
                 if (ok) ok = mbar_wait(v_full(s), (j / AT_STAGES) & 1, a.error, 12);
                 if (!ok) break;
                 tc_fence_after();
@@ -209,9 +229,9 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                 // 32 bytes along P's rows); N = dh spans KB column boxes of V
 #pragma unroll
                 for (int k = 0; k < AT_BN / 16; ++k) {
-                    const uint64_t dp = umma_desc(sp) + 2 * k;
+                    // P of tile j lies where S of tile j lay: 16 keys = 8 columns of packed pairs per step
                     const uint64_t dv = umma_desc_strides(sv + k * 2048, a.v_lbo, a.v_sbo);
-                    umma_bf16(tmem_o, dp, dv, idesc_o, (j | k) != 0);
+                    umma_bf16_ts(tmem_o, tmem_s + (j & 1) * AT_BN + 8 * k, dv, idesc_o, (j | k) != 0);
                 }
                 umma_commit(v_empty(s));
                 umma_commit(o_done);
@@ -275,13 +295,13 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                 pk[i / 2] = *reinterpret_cast<uint32_t*>(&hp);
             }
             l_run = l_run * rescale + (psum0 + psum1);
-            // the previous tile's P V must be done before P is overwritten and before O is touched
-            if (j > 0) {
+            // O may only be touched once the previous tile's P V is done (P itself goes where this tile's S was,
+            // which nothing reads any more: no wait for that)
+            const bool touch_o = __any_sync(0xffffffffu, rescale != 1.0f) && j > 0;
+            if (touch_o) {
                 ok = mbar_wait(o_done, (j - 1) & 1, a.error, 16);
                 tc_fence_after();
                 if (!ok) break;
-            }
-            if (__any_sync(0xffffffffu, rescale != 1.0f) && j > 0) {
 #pragma unroll
                 for (int c0 = 0; c0 < DH; c0 += 32) {
                     float o[32];
@@ -291,19 +311,19 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                     tmem_st32(tmem_o + lane_sel + c0, o);
                 }
             }
-            // into the A-operand tile [128 rows x 64 keys], 128-byte swizzle: row r at r * 128 bytes, its
-            // 16-byte chunk c at ((c ^ (r & 7)) * 16)
-            const uint32_t prow = sp + row * 128;
-#pragma unroll
-            for (int c = 0; c < AT_BN / 8; ++c)
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((c ^ (row & 7)) << 4)),
-                             "r"(pk[4 * c]), "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
-                             : "memory");
-            // make the generic-proxy writes of P visible to the tensor core (async proxy), then signal
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P as the A operand of the second product, in tensor memory: this row's 64 values as 32 packed pairs
+            // over the first 32 columns of the S buffer they came from
+            tmem_st32_words(tmem_s + (j & 1) * AT_BN + lane_sel, pk);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_ready) : "memory");
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_ready(j & 1)) : "memory");
+            // Keep in step with the products' completions, one phase at a time (a wait on a phase's parity cannot
+            // tell "two behind" from "done").  Here it costs nothing: P has been handed over, and the product
+            // waited for was issued a whole tile ago.
+            if (j > 0 && !touch_o) {
+                ok = mbar_wait(o_done, (j - 1) & 1, a.error, 16);
+                tc_fence_after();
+            }
         }
         if (ok) {
             ok = mbar_wait(o_done, (n_tiles - 1) & 1, a.error, 17);
@@ -336,7 +356,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
 template <int DH>
 static int attention_tc_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AtArgs& a,
                                cudaStream_t s) {
-    const size_t smem = (size_t)AT_BM * DH * 2 + AT_BM * AT_BN * 2 + (size_t)AT_STAGES * 2 * AT_BN * DH * 2 + 160;
+    const size_t smem = (size_t)AT_BM * DH * 2 + (size_t)AT_STAGES * 2 * AT_BN * DH * 2 + 160;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
