@@ -8,9 +8,11 @@
 //     one tcgen05.mma issued by the leader reads both blocks' operands and writes rows 0..127 of the product
 //     into the leader's tensor memory and rows 128..255 into the other's.  Per block and k-block that is 32 KB
 //     from L2 for 128 x 256 x 64 of product instead of 48 KB, and six ring stages fit instead of four.
-//     Measured: 1.61 against 1.53 PFLOP/s on 8192 x 4096 x 4096 and +7 % on experts with 2,048 rows each; but
-//     with few rows per group the 256-row tiles are mostly padding and there are half as many work items
-//     (decoding at batch 64: -7 %), so the launcher takes pairs only from 1,024 rows per group on;
+//     Measured when it went in: 1.61 against 1.53 PFLOP/s on 8192 x 4096 x 4096 and +7 % on experts with 2,048 rows
+//     each; with few rows per group the 256-row tiles are mostly padding and there are half as many work items
+//     (decoding at batch 64: -7 %).  Since the tiles of a group are numbered with its row tiles innermost (tc_tile)
+//     the single blocks share their B tiles through L2 just as well, and the launcher takes pairs only from 1,024
+//     rows per group on and for a short K (see tb_gemm_tc_bf16);
 //   * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of TC_STAGES stages;
 //     with pairs, both blocks' copies are counted on the LEADER's barrier of the stage;
 //   * tcgen05.commit (with pairs: multicast to both blocks) hands a finished stage back to the TMA warps and, after
@@ -541,8 +543,11 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     if (rc) return rc;
     int* err_ptr = tc_error_ptr();
     if (!err_ptr) return tb_last_error();
-    // pairs of blocks pay from about a thousand rows per group on (see the head of this file)
-    const bool pair = (long long)M >= 1024ll * G;
+    // Pairs of blocks pay from about a thousand rows per group on, and only with a short K (the experts' down
+    // product of narrow experts, K = 688: -9 % at 2,048 rows per group), where a tile is over after a few k-blocks
+    // and what counts is how few bytes its start needs.  With K = 4,096 both forms measure the same, and with wide
+    // experts (K or N of 14,336) the single blocks are 4..20 % faster (1.41 against 1.18 PFLOP/s at 2,048 rows).
+    const bool pair = (long long)M >= 1024ll * G && K < 2048;
     TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, 0, n_tile};
     rc = pair ? tc_launch<2>(ma, mb, a, s) : tc_launch<1>(ma, mb, a, s);
     if (pair && rc == TB_ERR_UNSUPPORTED) rc = tc_launch<1>(ma, mb, a, s);
