@@ -599,3 +599,42 @@ def test_weights_drawn_on_the_device_are_the_folders(dtype, tmp_path):
         for name, part in a.parts().items():
             for wname, w in part.weights.items():
                 assert torch.equal(w, b.parts()[name].weights[wname]), (name, wname)
+
+
+# ---------------------------------------------------------------------------------------------
+def test_attention_over_a_long_context():
+    """Twelve thousand cached tokens (188 scrambled pages), bfloat16, heads of 128: the tcgen05 and the mma.sync prompt
+    kernels continue a prompt by 300 tokens, the page-ring and the register-staged decode kernels take one token with
+    the keys cut into 1, 8 and 32 slices.  One early key (position 7) is scaled up so that a lost first page or slice
+    would show in every row."""
+    lib = _lib()
+    nh, nkvh, dh, dtype = 4, 2, 128, torch.bfloat16
+    scale = 1.0 / math.sqrt(dh)
+    # prompts: a long continuation, and a short sequence beside it
+    tq = lib.attention_tc_tile_tokens()
+    c = attention_case([300, 70], [11700, 0], nh, nkvh, dh, dtype, tq, seed=91, scale_key=(0, 7, 3.0))
+    nt = c["nt"]
+    out = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
+    assert lib.try_call("tb_attention_tc_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(), c["vc"].data_ptr(),
+                        c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(), c["tile_nq"].data_ptr(), c["tok_pos"].data_ptr(),
+                        c["table"].data_ptr(), c["tiles"], nt, c["max_pages"], nh * dh, nh, nkvh, dh, c["kc"].shape[0],
+                        scale)
+    assert lib.gemm_tc_status() == 0
+    assert float((out.double().cpu().reshape(nt, nh, dh) - c["ref"]).abs().max()) <= _tol(dtype, 4.0), "tcgen05 prompt kernel"
+    tq2 = lib.attention_prefill_tile_tokens()
+    c2 = attention_case([300, 70], [11700, 0], nh, nkvh, dh, dtype, tq2, seed=91, scale_key=(0, 7, 3.0))
+    out.zero_()
+    assert lib.try_call("tb_attention_prefill_bf16", c2["q"].data_ptr(), out.data_ptr(), c2["kc"].data_ptr(),
+                        c2["vc"].data_ptr(), c2["tile_seq"].data_ptr(), c2["tile_t0"].data_ptr(), c2["tile_nq"].data_ptr(),
+                        c2["tok_pos"].data_ptr(), c2["table"].data_ptr(), c2["tiles"], c2["max_pages"], nh * dh, nh,
+                        nkvh, dh, scale)
+    assert float((out.double().cpu().reshape(nt, nh, dh) - c2["ref"]).abs().max()) <= _tol(dtype, 4.0), "mma.sync prompt kernel"
+    # decoding: three sequences of 12,001, 8,192 and 4,096 tokens
+    d = attention_case([1, 1, 1], [12000, 8191, 4095], nh, nkvh, dh, dtype, 1, seed=92, scale_key=(0, 7, 3.0))
+    for splits in (1, 8, 32):
+        done = torch.zeros(3 * nh, dtype=torch.int32, device="cuda")
+        for tma, counters in ((True, done), (True, None), (False, None)):
+            got = _run_attention(lib, d, dtype, splits, decode=True, tma=tma, done=counters)
+            assert got is not None
+            assert float((got - d["ref"]).abs().max()) <= _tol(dtype, 4.0), f"decode, splits {splits}, ring {tma}"
+        assert int(done.abs().sum()) == 0
