@@ -87,3 +87,38 @@ def test_real_layer_through_cuda_graphs(models):
         outs.append([eng.step(slots, [[5 + j], [7 + j]]).cpu().clone() for j in range(5)])
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+LONG = {
+    "model_type": "llama", "num_hidden_layers": 1, "hidden_size": 4096, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 1024, "max_position_embeddings": 16384,
+    "vocab_size": 1000, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": False,
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_in_pieces_then_decoding(dtype):
+    """One real-size layer (grouped-query attention, dense feed-forward: no routing to tip) over 9,000 tokens: the
+    prompt exceeds the 8,192 tokens a step takes at once, so it runs as two pieces, the second attending over what the
+    first left in 128 pages of the cache; then three tokens one by one.  Logits at the first, a middle, the last position
+    of each piece and at every decoded token against the plain implementation (float64 on the GPU, the same weights
+    by the counter-based rule)."""
+    from plain import counter_weights as C
+    from plain import llama_moe_vectorized as PV
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    engine = tb.random_model(LONG, seed=21, dtype=dtype, std=0.02, max_tokens=9216, max_slots=1)
+    tensors = {n: v.double() for n, v in C.llama_tensors(LONG, 21, 0.02, engine.device, tdt).items()}
+    tokens = random_prompts(LONG["vocab_size"], [9003], seed=6)[0]
+    want = [0, 4095, 8191, 8192, 8600, 8999]
+    s = engine.open()
+    got = [engine.step([s], [tokens[:9000]], [want]).cpu()]
+    for t in tokens[9000:]:
+        got.append(engine.step([s], [[t]]).cpu())
+    engine.check_kernels()
+    engine.close(s)
+    got = torch.cat(got)
+    store = None if dtype == "float32" else (lambda x: x.bfloat16().to(x.dtype))
+    ref = PV.forward(LONG, tensors, tokens, want=want + [9000, 9001, 9002], store=store).float().cpu()
+    tol = 1e-4 if dtype == "float32" else 2.0 ** -6 * float(ref.abs().max())
+    worst = (got - ref).abs().max(dim=1).values
+    assert float(worst.max()) <= tol, f"per position {worst.tolist()} against {tol}"
