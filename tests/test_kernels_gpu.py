@@ -146,18 +146,18 @@ def test_rope_and_cache_write(dtype, pairing):
 
 
 # ---------------------------------------------------------------------------------------------
-def _run_attention(lib, c, dtype, splits, decode, tma=False, done=None):
+def _run_attention(lib, c, dtype, splits, decode, ring=False, done=None):
     nt, nh, dh = c["nt"], c["nh"], c["dh"]
     out = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
     partial = torch.empty(max(1, nt * nh * splits * (dh + 2)), dtype=torch.float32, device="cuda")
     scale = 1.0 / math.sqrt(dh)
     if decode:
         seq = torch.repeat_interleave(c["tile_seq"], c["tile_nq"])
-        if tma:
-            ok = lib.try_call("tb_attention_decode_tma_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
+        if ring:       # the kernel with a ring of cache pages: TMA, products on the tensor cores
+            ok = lib.try_call("tb_attention_decode_mma_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
                               c["vc"].data_ptr(), seq.data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(),
                               partial.data_ptr(), 0 if done is None else done.data_ptr(), nt, c["max_pages"], nh * dh,
-                              nh, c["nkvh"], dh, splits, scale)
+                              nh, c["nkvh"], dh, splits, c["kc"].shape[0], scale)
             assert lib.gemm_tc_status() == 0
             return out.double().cpu().reshape(nt, nh, dh) if ok else None
         ok = lib.try_call("tb_attention_decode_" + lib.suffix(dtype), c["q"].data_ptr(), out.data_ptr(),
@@ -537,30 +537,44 @@ def test_attention_tcgen05_kernel(nh, nkvh, dh):
     assert float((got - c["ref"]).abs().max()) <= _tol(dtype, 4.0)
 
 
-@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 64), (8, 8, 128), (12, 2, 64), (20, 2, 128), (3, 1, 128)])
-def test_attention_decode_tma(nh, nkvh, dh):
-    """The TMA-fed decode kernel: contexts of one token, exactly one page, a page and a bit, many pages;
-    key slices that leave some slices empty."""
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 4, 64), (8, 8, 128), (12, 2, 64), (20, 2, 128), (3, 1, 128), (32, 8, 128),
+                                        (16, 1, 64), (40, 2, 128), (51, 3, 64)])
+def test_attention_decode_on_tensor_cores(nh, nkvh, dh):
+    """The decode kernel whose products run as mma.sync with a group's query heads as rows: groups of 1, 3, 4, 6, 10,
+    exactly 16, 17 and 20 heads (more than 16 take two blocks); contexts of one token, exactly one page, a page and a
+    bit, many pages; key slices that leave some slices empty; both ways of merging the slices."""
     lib = _lib()
-    c = attention_case([1, 1, 1, 1, 1], [0, 63, 64, 700, 129], nh, nkvh, dh, torch.bfloat16, 1, seed=5 * nh + dh)
+    c = attention_case([1, 1, 1, 1, 1, 1], [0, 63, 64, 700, 129, 15], nh, nkvh, dh, torch.bfloat16, 1, seed=7 * nh + dh)
     for splits in (1, 2, 7):
-        done = torch.zeros(5 * nh, dtype=torch.int32, device="cuda")
-        for counters in (None, done, done):     # a merge kernel; the last block merges (twice: counters left at zero)
-            got = _run_attention(lib, c, torch.bfloat16, splits, decode=True, tma=True, done=counters)
+        done = torch.zeros(6 * nh, dtype=torch.int32, device="cuda")
+        for counters in (None, done, done):
+            got = _run_attention(lib, c, torch.bfloat16, splits, decode=True, ring=True, done=counters)
             assert got is not None
             assert float((got - c["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"splits {splits}"
             assert int(done.abs().sum()) == 0
     if (nh, nkvh, dh) == (12, 2, 64):
-        # many more blocks than fit the GPU at once, sequences of very unequal lengths
         pos = [(37 * i * i + 11 * i) % 900 for i in range(70)]
-        big = attention_case([1] * 70, pos, 16, 8, 64, torch.bfloat16, 1, seed=77)
-        done = torch.zeros(70 * 16, dtype=torch.int32, device="cuda")
+        big = attention_case([1] * 70, pos, 24, 4, 64, torch.bfloat16, 1, seed=78)
+        done = torch.zeros(70 * 24, dtype=torch.int32, device="cuda")
         for splits in (1, 5):
-            got = _run_attention(lib, big, torch.bfloat16, splits, decode=True, tma=True, done=done)
+            got = _run_attention(lib, big, torch.bfloat16, splits, decode=True, ring=True, done=done)
             assert float((got - big["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"70 sequences, splits {splits}"
             assert int(done.abs().sum()) == 0 and lib.gemm_tc_status() == 0
     c48 = attention_case([1], [10], 2, 1, 48, torch.bfloat16, 1, seed=1)
-    assert _run_attention(lib, c48, torch.bfloat16, 1, decode=True, tma=True) is None, "a head of 48 is refused"
+    assert _run_attention(lib, c48, torch.bfloat16, 1, decode=True, ring=True) is None, "a head of 48 is refused"
+
+
+def test_decode_on_tensor_cores_finds_one_far_key():
+    """Among 1,500 keys one (position 3, in the first page of the first slice, held by the first warp) is scaled so
+    that it takes nearly all the weight of every head; then one at the context's very end (the newest key, the last
+    row a warp reads before the mask).  A page, a warp's share of a page or a slice that was lost shows at once."""
+    lib = _lib()
+    for where in (3, 1499, 1087):
+        c = attention_case([1, 1], [1499, 1499], 12, 2, 128, torch.bfloat16, 1, seed=40 + where, scale_key=(0, where, 6.0))
+        for splits in (1, 4, 11):
+            done = torch.zeros(2 * 12, dtype=torch.int32, device="cuda")
+            got = _run_attention(lib, c, torch.bfloat16, splits, decode=True, ring=True, done=done)
+            assert float((got - c["ref"]).abs().max()) <= _tol(torch.bfloat16, 4.0), f"key {where}, splits {splits}"
 
 
 # ---------------------------------------------------------------------------------------------
@@ -633,8 +647,8 @@ def test_attention_over_a_long_context():
     d = attention_case([1, 1, 1], [12000, 8191, 4095], nh, nkvh, dh, dtype, 1, seed=92, scale_key=(0, 7, 3.0))
     for splits in (1, 8, 32):
         done = torch.zeros(3 * nh, dtype=torch.int32, device="cuda")
-        for tma, counters in ((True, done), (True, None), (False, None)):
-            got = _run_attention(lib, d, dtype, splits, decode=True, tma=tma, done=counters)
+        for ring, counters in ((True, done), (True, None), (False, None)):
+            got = _run_attention(lib, d, dtype, splits, decode=True, ring=ring, done=counters)
             assert got is not None
-            assert float((got - d["ref"]).abs().max()) <= _tol(dtype, 4.0), f"decode, splits {splits}, ring {tma}"
+            assert float((got - d["ref"]).abs().max()) <= _tol(dtype, 4.0), f"decode, splits {splits}, ring {ring}"
         assert int(done.abs().sum()) == 0

@@ -34,7 +34,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_attention_prefill_bf16": "pppppppppiiiiiif",
     "tb_attention_tc_bf16": "pppppppppiiiiiiiif",
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
-    "tb_attention_decode_tma_bf16": "pppppppppiiiiiiif",
+    "tb_attention_decode_mma_bf16": "pppppppppiiiiiiiif",
     "tb_router_f32": "pppppppppiiii", "tb_router_bf16": "pppppppppiiii",
     "tb_moe_dispatch": "ppppiii", "tb_topk_softmax": "pllppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",

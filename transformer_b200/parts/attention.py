@@ -17,7 +17,7 @@ from .spec import PartSpec
 
 
 USE_TCGEN05 = True     # prompts: the tcgen05 kernel before the mma.sync one
-USE_DECODE_TMA = True  # decoding: cache pages by TMA before the register-staged kernel
+USE_DECODE_RING = True  # decoding: the kernel with a ring of cache pages (TMA, tensor cores) before the register-staged one
 
 
 @MIXERS.register("attention")
@@ -122,25 +122,25 @@ class Attention(Mixer):
     def _decode_kernel(self, ctx, qkv, o, cache, table, nt, sfx) -> bool:
         """One token per sequence: the kernel that streams the cache.  False if it refuses the head size."""
         group = self.nh // self.nkvh
-        gc = 1 if group == 1 else 2 if group == 2 else 4
+        ring = USE_DECODE_RING and self.dtype == torch.bfloat16 and self.dh in (64, 128)
+        gc = 16 if ring else 1 if group == 1 else 2 if group == 2 else 4       # query heads of a group per block
         blocks = nt * self.nkvh * ((group + gc - 1) // gc)
         # Slices of the keys so that the blocks fill the GPU: as many blocks as are resident at once for the kernel
         # that keeps a ring of pages in shared memory (two per SM: measured best at batch 1 to 16, also with lengths
         # that differ 16-fold), eight times the SMs for the register-staged one.  A function of the batch's shape
         # alone, since a captured graph keeps it for as long as the sequences grow (the kernels cut short sequences
         # into fewer slices by themselves).
-        ring = USE_DECODE_TMA and self.dtype == torch.bfloat16 and self.dh in (64, 128)
         splits = int(max(1, min(32, ((2 if ring else 8) * ctx.engine.sm_count) // blocks)))
         partial = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
         if ring:
-            # counters of finished slices: the block that finishes a head's last slice merges them
+            # counters of finished slices: the block that finishes a head group's last slice merges them
             done = ctx.scratch("attn.done", (nt * self.nh,), torch.int32, zero=True) if splits > 1 else None
-            if lib.try_call("tb_attention_decode_tma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
-                            lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial),
-                            lib.ptr(done), nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits,
-                            self.scale):
+            if lib.try_call("tb_attention_decode_mma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k),
+                            lib.ptr(cache.v), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table),
+                            lib.ptr(partial), lib.ptr(done), nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh,
+                            self.dh, splits, cache.k.shape[0], self.scale):
                 return True
         return lib.try_call("tb_attention_decode_" + sfx, lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                             lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
