@@ -378,6 +378,60 @@ def test_router(dtype, E, k, d, nt):
         assert float((w[t].double().cpu() - weights).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("E,k,d,nt", [(16, 4, 4096, 2048), (8, 2, 96, 17), (6, 3, 64, 300), (24, 5, 1024, 1000),
+                                      (60, 7, 320, 333), (64, 64, 32, 16)])
+def test_router_for_many_tokens(E, k, d, nt):
+    """The router that takes 16 tokens' logits as one tensor-core tile: widths from one 32-column chunk (fewer
+    chunks than warps) to 4,096, expert counts that are no multiple of 8, a last block of 1, 5, 12 and 16 tokens;
+    logits against float64, the choice against the plain rule from the kernel's own logits, against the per-token
+    kernel, and the dispatch lists that its last block builds, twice."""
+    lib = _lib()
+    dtype = torch.bfloat16
+    x, wr = _rand((nt, d), dtype, 13), _rand((E, d), dtype, 14, 0.3)
+    idx = torch.empty((nt, k), dtype=torch.int32, device="cuda")
+    w = torch.empty((nt, k), dtype=torch.float32, device="cuda")
+    lg = torch.empty((nt, E), dtype=torch.float32, device="cuda")
+    lib.call("tb_router_rows_bf16", x.data_ptr(), wr.data_ptr(), idx.data_ptr(), w.data_ptr(), lg.data_ptr(), 0, 0, 0, 0,
+             nt, d, E, k)
+    ref_lg = x.double() @ wr.double().T
+    assert float((lg.double() - ref_lg).abs().max()) <= 2e-5 * max(1.0, float(ref_lg.abs().max())), \
+        "router logits are float whatever the storage type"
+    for t in list(range(0, nt, max(1, nt // 50))) + [nt - 1]:
+        experts, weights = P.route(lg[t].double().cpu(), k)     # from the kernel's own logits: exact rule
+        assert idx[t].tolist() == experts, t
+        assert float((w[t].double().cpu() - weights).abs().max()) < 1e-5
+    # the per-token kernel sums in another order: the same experts wherever its two candidates are a clear gap apart
+    idx1, w1, lg1 = torch.empty_like(idx), torch.empty_like(w), torch.empty_like(lg)
+    lib.call("tb_router_bf16", x.data_ptr(), wr.data_ptr(), idx1.data_ptr(), w1.data_ptr(), lg1.data_ptr(), 0, 0, 0, 0,
+             nt, d, E, k)
+    assert float((lg - lg1).abs().max()) <= 2e-5 * max(1.0, float(ref_lg.abs().max()))
+    top = torch.sort(lg, dim=1, descending=True).values
+    clear = ((top[:, :-1] - top[:, 1:])[:, :k].min(dim=1).values > 1e-4) if k < E else \
+        ((top[:, :-1] - top[:, 1:]).min(dim=1).values > 1e-4)
+    assert int(clear.sum()) > nt // 2
+    assert torch.equal(idx[clear], idx1[clear])
+    offs = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    tok = torch.empty(nt * k, dtype=torch.int32, device="cuda")
+    row = torch.empty(nt * k, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    idx2, w2 = torch.empty_like(idx), torch.empty_like(w)
+    for _ in range(2):
+        offs.fill_(-1), tok.fill_(-1), row.fill_(-1)
+        lib.call("tb_router_rows_bf16", x.data_ptr(), wr.data_ptr(), idx2.data_ptr(), w2.data_ptr(), 0,
+                 offs.data_ptr(), tok.data_ptr(), row.data_ptr(), done.data_ptr(), nt, d, E, k)
+        assert torch.equal(idx2, idx) and torch.equal(w2, w) and int(done) == 0
+        flat = idx.flatten().cpu()
+        counts = torch.bincount(flat, minlength=E)
+        assert offs.cpu().tolist() == [0] + torch.cumsum(counts, 0).tolist()
+        r = row.cpu().long()
+        assert sorted(r.tolist()) == list(range(nt * k)), "every pair has a row of its own"
+        assert torch.equal(tok.cpu()[r], torch.arange(nt * k, dtype=torch.int32) // k), "a row reads its pair's token"
+        e_of_row = torch.bucketize(r, offs.cpu().long()[1:], right=True)
+        assert torch.equal(e_of_row, flat.long()), "a pair's row lies in its expert's range"
+    assert not lib.try_call("tb_router_rows_bf16", x.data_ptr(), wr.data_ptr(), idx.data_ptr(), w.data_ptr(), 0, 0, 0, 0, 0,
+                            nt, 40, E, k), "a width that is no multiple of 32 is refused"
+
+
 def test_router_ties_go_to_the_lower_expert():
     lib = _lib()
     E, k, d = 8, 3, 16

@@ -36,7 +36,8 @@ _SIGNATURES: Dict[str, str] = {
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
     "tb_attention_decode_mma_bf16": "pppppppppiiiiiiiif",
     "tb_router_f32": "pppppppppiiii", "tb_router_bf16": "pppppppppiiii",
-    "tb_moe_dispatch": "ppppiii", "tb_topk_softmax": "pllppiii",
+    "tb_router_rows_bf16": "pppppppppiiii",
+    "tb_moe_dispatch": "ppppiii",
     "tb_moe_combine_f32": "ppppiii", "tb_moe_combine_bf16": "ppppiii",
     "tb_sample": "plpiififpp",
     "tb_kernel_status_async": "p",

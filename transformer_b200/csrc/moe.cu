@@ -106,21 +106,113 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
     dispatch_lists(topk_idx, lists.group_offsets, lists.sorted_token, lists.pair_row, nt * k, k, E, count, cursor);
 }
 
-// Top-k and weights from router logits that are already in memory: one warp per token.  The logit of
-// (token t, expert e) is at logits[t * ld_t + e * ld_e], so both [nt, E] and [E, nt] layouts serve.
-// Same rules as router_kernel; used when the logits come from a matrix-product kernel.
-__global__ void __launch_bounds__(128)
-topk_softmax_kernel(const float* __restrict__ logits, long long ld_t, long long ld_e, int* __restrict__ topk_idx,
-                    float* __restrict__ topk_w, int nt, int E, int k) {
-    pdl_sync();
-    extern __shared__ float lg_all[];   // [4][E]
+// Many tokens, bfloat16: the logits of 16 tokens x up to 64 experts are tiles of mma.sync.m16n8k16, accumulated in
+// float.  A block's eight warps split the width; every lane reads 16 bytes (8 values) of its token's row and of its
+// expert's row per 32 columns and feeds them to two k-steps: which of the 16 k-slots of an instruction a value sits
+// in does not matter as long as the token's and the expert's value of one column sit in the same slot.  The
+// activations are read once (the per-token kernel above reads the router's matrix once per token).  The warps' sums
+// meet in shared memory, are added in a fixed order, and the same router_pick finishes each token, a warp per token.
+#define RR_ROWS 16
+
+template <int NT, int RR_WARPS>   // tiles of 8 experts; warps that split the width
+__global__ void __launch_bounds__(RR_WARPS * 32)
+router_rows_kernel(const __nv_bfloat16* __restrict__ x1, const __nv_bfloat16* __restrict__ wr,
+                   int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d,
+                   int E, int k, const DispatchLists lists) {
+    constexpr int EP = 8 * NT;
+    constexpr int U = NT <= 2 ? 4 : NT == 4 ? 2 : 1;     // chunks of 32 columns in flight per warp
+    __shared__ float part[RR_WARPS][RR_ROWS][EP + 1];
+    __shared__ int count[ROUTER_MAX_E + 1];
+    __shared__ int cursor[ROUTER_MAX_E];
+    __shared__ bool last_block;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= nt) return;
-    float* lg = lg_all + warp * E;
-    for (int e = lane; e < E; e += 32) lg[e] = logits[(size_t)t * ld_t + (size_t)e * ld_e];
-    __syncwarp();
-    router_pick(lg, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+    const int g = lane >> 2, t4 = lane & 3;
+    const int row0 = blockIdx.x * RR_ROWS;
+    const int chunks = d / 32;
+    const bool lo = row0 + g < nt, hi = row0 + g + 8 < nt;
+    const __nv_bfloat16* xa = x1 + (size_t)(row0 + g) * d + t4 * 8;
+    const __nv_bfloat16* xb = xa + (size_t)8 * d;
+    const __nv_bfloat16* wb = wr + (size_t)g * d + t4 * 8;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    // the router's rows of this warp's first chunks do not depend on the kernel before: read before the wait
+    uint4 wv[U][NT];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int c = warp + u * RR_WARPS;
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+            wv[u][j] = (c < chunks && 8 * j + g < E) ? *reinterpret_cast<const uint4*>(wb + (size_t)8 * j * d + c * 32) : zero;
+    }
+    pdl_sync();
+    for (int c0 = warp; c0 < chunks; c0 += RR_WARPS * U) {
+        uint4 av[U], bv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + u * RR_WARPS;
+            av[u] = (lo && c < chunks) ? *reinterpret_cast<const uint4*>(xa + c * 32) : zero;
+            bv[u] = (hi && c < chunks) ? *reinterpret_cast<const uint4*>(xb + c * 32) : zero;
+            if (c0 != warp) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+                    wv[u][j] = (c < chunks && 8 * j + g < E)
+                                   ? *reinterpret_cast<const uint4*>(wb + (size_t)8 * j * d + c * 32) : zero;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                asm volatile(
+                    "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                    : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                    : "r"(av[u].x), "r"(bv[u].x), "r"(av[u].y), "r"(bv[u].y), "r"(wv[u][j].x), "r"(wv[u][j].y));
+                asm volatile(
+                    "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                    : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                    : "r"(av[u].z), "r"(bv[u].z), "r"(av[u].w), "r"(bv[u].w), "r"(wv[u][j].z), "r"(wv[u][j].w));
+            }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        part[warp][g][8 * j + 2 * t4] = acc[j][0];
+        part[warp][g][8 * j + 2 * t4 + 1] = acc[j][1];
+        part[warp][g + 8][8 * j + 2 * t4] = acc[j][2];
+        part[warp][g + 8][8 * j + 2 * t4 + 1] = acc[j][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < RR_ROWS * EP; i += RR_WARPS * 32) {
+        const int r = i / EP, e = i - r * EP;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < RR_WARPS; ++w) v += part[w][r][e];
+        part[0][r][e] = v;
+        if (logits_out && row0 + r < nt && e < E) logits_out[(size_t)(row0 + r) * E + e] = v;
+    }
+    __syncthreads();
+    if (k <= ROUTER_PICK_SERIAL_K && E * k <= 256) {
+        const int t = row0 + (int)threadIdx.x;
+        if (threadIdx.x < RR_ROWS && t < nt)
+            router_pick_serial(&part[0][threadIdx.x][0], topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k);
+    } else {
+        for (int r = warp; r < RR_ROWS; r += RR_WARPS) {
+            const int t = row0 + r;
+            if (t < nt) router_pick(&part[0][r][0], topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+        }
+    }
+    if (!lists.done) return;
+    __threadfence();          // these tokens' choices are visible before the count says so
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last_block = atomicAdd(lists.done, 1u) == gridDim.x - 1;
+        if (last_block) *lists.done = 0;
+    }
+    __syncthreads();
+    if (!last_block) return;
+    __threadfence();
+    dispatch_lists(topk_idx, lists.group_offsets, lists.sorted_token, lists.pair_row, nt * k, k, E, count, cursor);
 }
 
 // One block builds the dispatch lists for M = nt * k (token, choice) pairs:
@@ -239,12 +331,22 @@ int tb_router_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w,
     return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k,
                                         DispatchLists{group_offsets, sorted_token, pair_row, done}, s);
 }
-int tb_topk_softmax(const float* logits, long long ld_t, long long ld_e, int* topk_idx, float* topk_w, int nt, int E, int k,
-                    cudaStream_t s) {
-    if (nt < 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
-    if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
+// Router for many tokens (bfloat16, up to 64 experts, a width that is a multiple of 32); `done` as in tb_router_*.
+int tb_router_rows_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out,
+                        int* group_offsets, int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E,
+                        int k, cudaStream_t s) {
+    if (nt < 0 || d <= 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
+    if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
+    if (E > 64 || d % 32 || (((uintptr_t)x1 | (uintptr_t)wr) & 15)) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
-    TB_LAUNCH((topk_softmax_kernel), (nt + 3) / 4, 128, (size_t)4 * E * sizeof(float), s, logits, ld_t, ld_e, topk_idx, topk_w, nt, E, k);
+    const DispatchLists lists{group_offsets, sorted_token, pair_row, done};
+    const int grid = (nt + RR_ROWS - 1) / RR_ROWS;
+    const __nv_bfloat16* x = (const __nv_bfloat16*)x1;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)wr;
+    if (E <= 8) TB_LAUNCH((router_rows_kernel<1, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
+    else if (E <= 16) TB_LAUNCH((router_rows_kernel<2, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
+    else if (E <= 32) TB_LAUNCH((router_rows_kernel<4, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
+    else TB_LAUNCH((router_rows_kernel<8, 8>), grid, 256, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
     return tb_last_error();
 }
 int tb_moe_dispatch(const int* topk_idx, int* group_offsets, int* sorted_token, int* pair_row, int M, int k, int E,
@@ -268,7 +370,7 @@ int tb_moe_combine_bf16(const void* y, const int* pair_row, const float* topk_w,
 #include "tape.h"
 TB_TAPE_REGISTER(tb_router_f32)
 TB_TAPE_REGISTER(tb_router_bf16)
-TB_TAPE_REGISTER(tb_topk_softmax)
+TB_TAPE_REGISTER(tb_router_rows_bf16)
 TB_TAPE_REGISTER(tb_moe_dispatch)
 TB_TAPE_REGISTER(tb_moe_combine_f32)
 TB_TAPE_REGISTER(tb_moe_combine_bf16)

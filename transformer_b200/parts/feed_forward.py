@@ -14,7 +14,7 @@ from .base import FEED_FORWARDS, FeedForward, NormTail, ParamDecl, WeightedRows
 from . import linear
 from .linear import gemm_skinny, grouped_matmul, matmul_nt
 
-ROUTER_PRODUCT_ROWS = 256   # above this many tokens the router logits come from the prompt product kernel
+ROUTER_ROWS_FROM = 256      # above this many tokens the router works on tiles of 16 tokens (tensor cores)
 ROUTER_TAIL_ROWS = 256      # up to this many tokens the norm before the experts also routes
 
 
@@ -79,16 +79,17 @@ class MoE(FeedForward):
         nt = x1.shape[0]
         idx = ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32)
         w = ctx.scratch("moe.topk_w", (nt, self.k), torch.float32)
-        if self.dtype == torch.bfloat16 and nt > ROUTER_PRODUCT_ROWS and logits_out is None and self.E <= 64:
-            # many tokens, few experts: the logits are a product whose long operand is the ACTIVATIONS, so the
-            # decode product kernel streams x1 once with the roles swapped (experts as its few "tokens"),
-            # float accumulation and output [E, nt]; one small kernel then picks the experts
-            lg = ctx.scratch("moe.logits", (self.E, nt), torch.float32)
-            if gemm_skinny(self.weights["router"], x1, lg, out_kind=1, w_is_weight=False):
-                lib.call("tb_topk_softmax", lib.ptr(lg), 1, nt, lib.ptr(idx), lib.ptr(w), nt, self.E, self.k)
-                return idx, w, False
+        if self.dtype == torch.bfloat16 and nt > ROUTER_ROWS_FROM and self.E <= 64:
+            # many tokens, few experts: 16 tokens' logits are a tensor-core tile, the activations are read once, and
+            # the block that finishes last builds the dispatch lists
+            done = ctx.scratch("moe.done", (1,), torch.int32, zero=True) if lists is not None else None
+            offsets, sorted_token, pair_row = lists if lists is not None else (None, None, None)
+            if lib.try_call("tb_router_rows_bf16", lib.ptr(x1), lib.ptr(self.weights["router"]), lib.ptr(idx), lib.ptr(w),
+                            lib.ptr(logits_out), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
+                            lib.ptr(done), nt, self.d, self.E, self.k):
+                return idx, w, lists is not None
         # a few tokens: the block that finishes last builds the lists, which saves a kernel on the way to the experts
-        fused = lists is not None and nt <= ROUTER_PRODUCT_ROWS
+        fused = lists is not None and nt <= ROUTER_ROWS_FROM
         done = ctx.scratch("moe.done", (1,), torch.int32, zero=True) if fused else None
         offsets, sorted_token, pair_row = lists if fused else (None, None, None)
         lib.call("tb_router_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
