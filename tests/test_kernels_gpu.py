@@ -618,6 +618,74 @@ def test_attention_decode_on_tensor_cores(nh, nkvh, dh):
     assert _run_attention(lib, c48, torch.bfloat16, 1, decode=True, ring=True) is None, "a head of 48 is refused"
 
 
+@pytest.mark.parametrize("pairing", ["adjacent", "half"])
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 4, 64), (8, 2, 128), (12, 2, 64), (40, 2, 128), (3, 1, 128)])
+def test_decode_attention_that_also_rotates_and_writes_the_cache(nh, nkvh, dh, pairing):
+    """The fused form against the two kernels it stands for (rotary kernel, then the attention over the finished
+    cache), from the same unrotated q-k-v rows: the same output, the same cache rows written, q-k-v left alone; with
+    the new rows poisoned in the cache beforehand, so that a kernel that read them from there would show; and against
+    float64 attention over the cache that the rotary kernel left.  Then for a layer that reads another layer's cache
+    (nothing to write: only the queries are rotated)."""
+    lib = _lib()
+    dtype = torch.bfloat16
+    pos = [0, 63, 64, 700, 129, 15]
+    c = attention_case([1] * len(pos), pos, nh, nkvh, dh, dtype, 1, seed=11 * nh + dh)
+    nt, width = c["nt"], (nh + 2 * nkvh) * dh
+    qkv = _rand((nt, width), dtype, 21)
+    theta = 10000.0
+    i = torch.arange(dh // 2, dtype=torch.float64)
+    ang = torch.arange(1024, dtype=torch.float64)[:, None] * theta ** (-2.0 * i / dh)[None]
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    half = 1 if pairing == "half" else 0
+    seq = torch.repeat_interleave(c["tile_seq"], c["tile_nq"])
+    scale = 1.0 / math.sqrt(dh)
+    # the two kernels
+    qkv_a, kc_a, vc_a = qkv.clone(), c["kc"].clone(), c["vc"].clone()
+    lib.call("tb_rope_cache_bf16", qkv_a.data_ptr(), seq.data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(),
+             c["max_pages"], cos.data_ptr(), sin.data_ptr(), kc_a.data_ptr(), vc_a.data_ptr(), nt, nh, nkvh, dh, half)
+    # float64 attention over that cache
+    ref = torch.zeros(nt, nh, dh, dtype=torch.float64)
+    table = c["table"].cpu()
+    q_rot = qkv_a[:, :nh * dh].double().cpu().reshape(nt, nh, dh)
+    for t in range(nt):
+        n = pos[t] + 1
+        pages = table[t, :(n + 63) // 64].long()
+        k = kc_a[pages.cuda()].double().cpu().permute(1, 0, 2, 3).reshape(nkvh, -1, dh)[:, :n]
+        v = vc_a[pages.cuda()].double().cpu().permute(1, 0, 2, 3).reshape(nkvh, -1, dh)[:, :n]
+        for h in range(nh):
+            g = h // (nh // nkvh)
+            ref[t, h] = torch.softmax(k[g] @ q_rot[t, h] * scale, 0) @ v[g]
+    poison_k, poison_v = c["kc"].clone(), c["vc"].clone()
+    for t in range(nt):
+        page = int(table[t, pos[t] // 64])
+        poison_k[page, :, pos[t] % 64] = 300.0
+        poison_v[page, :, pos[t] % 64] = -300.0
+    for splits in (1, 2, 7):
+        partial = torch.empty(nt * nh * splits * (dh + 2), dtype=torch.float32, device="cuda")
+        done = torch.zeros(nt * nh, dtype=torch.int32, device="cuda")
+        out_a = torch.zeros(nt, nh * dh, dtype=dtype, device="cuda")
+        lib.call("tb_attention_decode_mma_bf16", qkv_a.data_ptr(), out_a.data_ptr(), kc_a.data_ptr(), vc_a.data_ptr(),
+                 seq.data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(), partial.data_ptr(), done.data_ptr(), nt,
+                 c["max_pages"], width, nh, nkvh, dh, splits, kc_a.shape[0], scale)
+        for write in (1, 0):
+            qkv_b = qkv.clone()
+            kc_b, vc_b = (poison_k.clone(), poison_v.clone()) if write else (kc_a.clone(), vc_a.clone())
+            out_b = torch.zeros_like(out_a)
+            lib.call("tb_attention_decode_rope_bf16", qkv_b.data_ptr(), out_b.data_ptr(), kc_b.data_ptr(), vc_b.data_ptr(),
+                     seq.data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(), partial.data_ptr(), done.data_ptr(),
+                     cos.data_ptr(), sin.data_ptr(), nt, c["max_pages"], width, nh, nkvh, dh, splits, kc_b.shape[0], half,
+                     write, scale)
+            assert lib.gemm_tc_status() == 0 and int(done.abs().sum()) == 0
+            assert torch.equal(qkv_b, qkv), "the q-k-v rows are read, not rotated in place"
+            assert torch.equal(vc_b, vc_a), "the value rows written are the rotary kernel's"
+            # the rotated key: the same arithmetic in another kernel, at most the last bit of a bfloat16 apart
+            dk = (kc_b.float() - kc_a.float()).abs()
+            assert float((dk / kc_a.float().abs().clamp_min(1e-3)).max()) <= 2.0 ** -7, "key rows written"
+            got = out_b.double().cpu().reshape(nt, nh, dh)
+            assert float((got - ref).abs().max()) <= _tol(dtype, 4.0), f"splits {splits}, write {write}"
+            assert float((out_b.float() - out_a.float()).abs().max()) <= _tol(dtype, 1.0), "against the two kernels"
+
+
 def test_decode_on_tensor_cores_finds_one_far_key():
     """Among 1,500 keys one (position 3, in the first page of the first slice, held by the first warp) is scaled so
     that it takes nearly all the weight of every head; then one at the context's very end (the newest key, the last

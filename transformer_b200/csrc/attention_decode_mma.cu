@@ -22,6 +22,11 @@
 //                                                                   bfloat16, are already laid out as an A operand;
 //                                                                   B = V by ldmatrix.trans)
 //
+// The fused form (FUSE) also does what the rotary kernel does for a decode step, so that a layer has one launch
+// less: the queries are rotated as they are loaded into registers; the new token's key (rotated) and value are taken
+// from the q-k-v product's result, laid over the row of the last page in shared memory that TMA brought in its old
+// state, and written to the cache by the block of the group's first 16 heads.  The producer then waits for nothing.
+//
 // Each of the four arithmetic warps takes 16 of a page's 64 keys and keeps a running (max, sum, O) of its own; they
 // are merged once at the end, in the ring's memory.  With the keys in slices, the block that finishes a (token, head
 // group)'s last slice merges the slices (a counter per group), so no kernel of its own is needed for that.
@@ -44,7 +49,24 @@ struct DecodeMmaArgs {
     int* error;
     int max_pages, q_stride, nh, nkvh, splits, stages;
     float scale_log2e;
+    // fused rotary encoding and cache write (FUSE): angle tables [positions, dh / 2]; pairing (i, i + dh/2) or
+    // (2i, 2i + 1); patch: the new token's key and value come from the row of q (behind the query heads) and go to
+    // kc_out / vc_out; without patch they are in the cache already (a layer that reads another layer's cache)
+    const float* cos_t;
+    const float* sin_t;
+    __nv_bfloat16* kc_out;
+    __nv_bfloat16* vc_out;
+    int half_pairing, patch;
 };
+
+__device__ __forceinline__ float2 dm_unpack(uint32_t v) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
+// (x0, x1) turned by the angle whose cosine and sine are c and s
+__device__ __forceinline__ void dm_turn(float x0, float x1, float c, float s, float& y0, float& y1) {
+    y0 = x0 * c - x1 * s;
+    y1 = x0 * s + x1 * c;
+}
 
 __device__ __forceinline__ void dm_ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -70,7 +92,7 @@ __device__ __forceinline__ uint32_t dm_at(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * (TB_PAGE * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-template <int DH>
+template <int DH, bool FUSE>
 __global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv,
                             const DecodeMmaArgs a) {
@@ -133,7 +155,8 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
             if (lane == 0) {
                 if (i >= S) ok = mbar_wait(empty_bar(s), ((i / S) - 1) & 1, a.error, 25);
                 if (ok) {
-                    if (!waited && p_lo + i == n_pages - 1) {   // the page the kernel before this one wrote to
+                    // the page a kernel of this step wrote to (fused: this block lays the new row over it itself)
+                    if (!(FUSE && a.patch) && !waited && p_lo + i == n_pages - 1) {
                         asm volatile("griddepcontrol.wait;" ::: "memory");
                         waited = true;
                     }
@@ -157,7 +180,59 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
         uint32_t qa[KS][4];
 #pragma unroll
         for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+        // Fused: the angles of this token's position were there before the step began; they are read before the
+        // wait, the q-k-v row's new key and value (by the warp that owns their row of the last page) right after it.
+        float ang[FUSE ? KS * 4 : 1];                     // this thread's cosines and sines for the queries
+        float pc[2] = {1.f, 1.f}, ps[2] = {0.f, 0.f};     // and for pairs lane, lane + 32 of the new key
+        const bool patcher = FUSE && a.patch && p_hi == n_pages && np > 0 && warp == (pos % TB_PAGE) / 16;
+        if (FUSE) {
+            const float* cs = a.cos_t + (size_t)pos * (DH / 2);
+            const float* sn = a.sin_t + (size_t)pos * (DH / 2);
+            if (a.half_pairing) {
+#pragma unroll
+                for (int ks = 0; ks < KS / 2; ++ks)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int i = 16 * ks + c2 + 8 * hh;
+                        const float2 c = *reinterpret_cast<const float2*>(cs + i);
+                        const float2 sv2 = *reinterpret_cast<const float2*>(sn + i);
+                        float* dst = ang + (ks * 2 + hh) * 4;
+                        dst[0] = c.x, dst[1] = c.y, dst[2] = sv2.x, dst[3] = sv2.y;
+                    }
+            } else {
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int i = 8 * ks + (c2 >> 1) + 4 * hh;
+                        ang[(ks * 2 + hh) * 2] = cs[i];
+                        ang[(ks * 2 + hh) * 2 + 1] = sn[i];
+                    }
+            }
+            if (patcher) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                    if (lane + 32 * u < DH / 2) {
+                        pc[u] = cs[lane + 32 * u];
+                        ps[u] = sn[lane + 32 * u];
+                    }
+            }
+        }
         asm volatile("griddepcontrol.wait;" ::: "memory");     // the queries come from the kernel before
+        float kx0[2] = {0.f, 0.f}, kx1[2] = {0.f, 0.f};
+        uint4 vnew = make_uint4(0u, 0u, 0u, 0u);
+        if (patcher) {
+            const __nv_bfloat16* kn = a.q + (size_t)t * a.q_stride + (size_t)(a.nh + g) * DH;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int p = lane + 32 * u;
+                if (p < DH / 2) {
+                    kx0[u] = __bfloat162float(kn[a.half_pairing ? p : 2 * p]);
+                    kx1[u] = __bfloat162float(kn[a.half_pairing ? p + DH / 2 : 2 * p + 1]);
+                }
+            }
+            if (lane < DH / 8) vnew = *reinterpret_cast<const uint4*>(kn + (size_t)a.nkvh * DH + lane * 8);
+        }
         const __nv_bfloat16* qg = a.q + (size_t)t * a.q_stride + (size_t)h0 * DH + c2;
         const bool lo = r0 < nheads, hi = r0 + 8 < nheads;
 #pragma unroll
@@ -169,6 +244,41 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
             qa[ks][2] = lo ? *reinterpret_cast<const uint32_t*>(q0 + 8) : 0u;
             qa[ks][3] = hi ? *reinterpret_cast<const uint32_t*>(q1 + 8) : 0u;
         }
+        if (FUSE) {
+            if (a.half_pairing) {
+                // dims d and d + DH/2 make a pair: the same register slot, KS/2 k-steps apart
+#pragma unroll
+                for (int ks = 0; ks < KS / 2; ++ks)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const float* an = ang + (ks * 2 + hh) * 4;
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            const float2 xl = dm_unpack(qa[ks][2 * hh + rr]), xh = dm_unpack(qa[ks + KS / 2][2 * hh + rr]);
+                            float l0, l1, h0f, h1f;
+                            dm_turn(xl.x, xh.x, an[0], an[2], l0, h0f);
+                            dm_turn(xl.y, xh.y, an[1], an[3], l1, h1f);
+                            qa[ks][2 * hh + rr] = dm_pack(l0, l1);
+                            qa[ks + KS / 2][2 * hh + rr] = dm_pack(h0f, h1f);
+                        }
+                    }
+            } else {
+                // dims 2i and 2i + 1 make a pair: the two halves of one register
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const float c = ang[(ks * 2 + hh) * 2], sv1 = ang[(ks * 2 + hh) * 2 + 1];
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            const float2 x = dm_unpack(qa[ks][2 * hh + rr]);
+                            float y0, y1;
+                            dm_turn(x.x, x.y, c, sv1, y0, y1);
+                            qa[ks][2 * hh + rr] = dm_pack(y0, y1);
+                        }
+                    }
+            }
+        }
         const int mi = lane >> 3, lr = lane & 7;
         const int krow = 16 * warp + (mi >> 1) * 8 + lr, kch = mi & 1;     // K: matrices (keys lo/hi) x (channels lo/hi)
         const int vrow = 16 * warp + (mi & 1) * 8 + lr, vch = mi >> 1;     // V: matrices (channels lo/hi) x (keys lo/hi)
@@ -177,6 +287,36 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
             ok = mbar_wait(full_bar(s), (i / S) & 1, a.error, 26);
             if (!ok) break;
             const uint32_t sk = smem_base + s * STAGE_BYTES, sv = sk + PAGE_BYTES;
+            if (patcher && i == np - 1) {
+                // The newest key and value: into this page's row in shared memory (only this warp reads that row),
+                // and into the cache by the block of the group's first heads.
+                const int row = pos % TB_PAGE, half = DH / 2;
+                uint8_t* pk = smem_al + (size_t)s * STAGE_BYTES;
+                uint8_t* pv = pk + PAGE_BYTES;
+                const bool writer = blockIdx.y % chunks == 0;
+                const size_t at = (((size_t)pt[n_pages - 1] * a.nkvh + g) * TB_PAGE + row) * DH;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int p = lane + 32 * u;
+                    if (p < half) {
+                        const int d0 = a.half_pairing ? p : 2 * p, d1 = a.half_pairing ? p + half : 2 * p + 1;
+                        float y0, y1;
+                        dm_turn(kx0[u], kx1[u], pc[u], ps[u], y0, y1);
+                        const __nv_bfloat16 b0 = __float2bfloat16_rn(y0), b1 = __float2bfloat16_rn(y1);
+                        *reinterpret_cast<__nv_bfloat16*>(pk + dm_at(row, d0 >> 3) + (d0 & 7) * 2) = b0;
+                        *reinterpret_cast<__nv_bfloat16*>(pk + dm_at(row, d1 >> 3) + (d1 & 7) * 2) = b1;
+                        if (writer) {
+                            a.kc_out[at + d0] = b0;
+                            a.kc_out[at + d1] = b1;
+                        }
+                    }
+                }
+                if (lane < DH / 8) {                       // the value: 16 bytes per lane
+                    *reinterpret_cast<uint4*>(pv + dm_at(row, lane)) = vnew;
+                    if (writer) *reinterpret_cast<uint4*>(a.vc_out + at + lane * 8) = vnew;
+                }
+                __syncwarp();
+            }
             float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
@@ -309,7 +449,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
     }
 }
 
-template <int DH>
+template <int DH, bool FUSE>
 static int decode_mma_launch(const CUtensorMap& mk, const CUtensorMap& mv, DecodeMmaArgs a, int nt, cudaStream_t s) {
     const size_t stage = (size_t)2 * TB_PAGE * DH * 2;
     const size_t tail = 2 * DM_MAX_STAGES * 8 + (size_t)2 * DM_WARPS * DM_HEADS * sizeof(float);
@@ -323,27 +463,27 @@ static int decode_mma_launch(const CUtensorMap& mk, const CUtensorMap& mv, Decod
     const size_t smem = stage * stages + tail + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DH>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DH, FUSE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int group = a.nh / a.nkvh;
     dim3 grid(nt, a.nkvh * ((group + DM_HEADS - 1) / DM_HEADS), a.splits);
-    TB_LAUNCH((attention_decode_mma_kernel<DH>), grid, DM_THREADS, smem, s, mk, mv, a);
+    TB_LAUNCH((attention_decode_mma_kernel<DH, FUSE>), grid, DM_THREADS, smem, s, mk, mv, a);
     return tb_last_error();
 }
 
-// q: [nt, q_stride] (first q head of each token), out: [nt, nh * dh], kc / vc: one layer's cache
-// [cache_pages, nkvh, 64, dh]; done: [nt * nkvh * ceil(group / 16)] zeroed counters, or null (then a merge kernel runs).
-extern "C" int tb_attention_decode_mma_bf16(const void* q, void* out, const void* kc, const void* vc, const int* tok_seq,
-                                            const int* tok_pos, const int* page_table, float* partial,
-                                            unsigned* done, int nt, int max_pages, int q_stride, int nh, int nkvh, int dh,
-                                            int splits, int cache_pages, float scale, cudaStream_t s) {
+static int decode_mma(const void* q, void* out, void* kc, void* vc, const int* tok_seq, const int* tok_pos,
+                      const int* page_table, float* partial, unsigned* done, const float* cos_t, const float* sin_t,
+                      int nt, int max_pages, int q_stride, int nh, int nkvh, int dh, int splits, int cache_pages,
+                      int half_pairing, int patch, bool fuse, float scale, cudaStream_t s) {
     if (nh <= 0 || nkvh <= 0 || nh % nkvh || splits < 1 || cache_pages <= 0) return TB_ERR_ARG;
     if (splits > 1 && !partial) return TB_ERR_ARG;
+    if (fuse && !(cos_t && sin_t)) return TB_ERR_ARG;
     if (dh != 64 && dh != 128) return TB_ERR_UNSUPPORTED;
     if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) & 15)) return TB_ERR_UNSUPPORTED;
+    if (fuse && (((uintptr_t)cos_t | (uintptr_t)sin_t) & 7)) return TB_ERR_UNSUPPORTED;
     if (nt <= 0) return nt == 0 ? 0 : TB_ERR_ARG;
     CUtensorMap mk, mv;
     const long long rows = (long long)cache_pages * nkvh * TB_PAGE;
@@ -355,8 +495,10 @@ extern "C" int tb_attention_decode_mma_bf16(const void* q, void* out, const void
     int* err = tc_error_ptr();
     if (!err) return tb_last_error();
     DecodeMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_seq, tok_pos, page_table, partial, done, err,
-                    max_pages, q_stride, nh, nkvh, splits, 0, scale * 1.4426950408889634f};
-    rc = dh == 64 ? decode_mma_launch<64>(mk, mv, a, nt, s) : decode_mma_launch<128>(mk, mv, a, nt, s);
+                    max_pages, q_stride, nh, nkvh, splits, 0, scale * 1.4426950408889634f,
+                    cos_t, sin_t, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, half_pairing, patch};
+    if (fuse) rc = dh == 64 ? decode_mma_launch<64, true>(mk, mv, a, nt, s) : decode_mma_launch<128, true>(mk, mv, a, nt, s);
+    else rc = dh == 64 ? decode_mma_launch<64, false>(mk, mv, a, nt, s) : decode_mma_launch<128, false>(mk, mv, a, nt, s);
     if (rc) return rc;
     if (splits > 1 && !done) {
         dim3 grid(nt, nh);
@@ -367,6 +509,33 @@ extern "C" int tb_attention_decode_mma_bf16(const void* q, void* out, const void
     return rc;
 }
 
+extern "C" {
+// q: [nt, q_stride] (first q head of each token, already rotated), out: [nt, nh * dh], kc / vc: one layer's cache
+// [cache_pages, nkvh, 64, dh] with the new token's key and value in it; done: [nt * nkvh * ceil(group / 16)] zeroed
+// counters, or null (then a merge kernel runs).
+int tb_attention_decode_mma_bf16(const void* q, void* out, const void* kc, const void* vc, const int* tok_seq,
+                                 const int* tok_pos, const int* page_table, float* partial, unsigned* done, int nt,
+                                 int max_pages, int q_stride, int nh, int nkvh, int dh, int splits, int cache_pages,
+                                 float scale, cudaStream_t s) {
+    return decode_mma(q, out, const_cast<void*>(kc), const_cast<void*>(vc), tok_seq, tok_pos, page_table, partial, done,
+                      nullptr, nullptr, nt, max_pages, q_stride, nh, nkvh, dh, splits, cache_pages, 0, 0, false, scale, s);
+}
+// The same with the rotary encoding and the cache write of a decode step inside: qkv is the q-k-v product's result
+// [nt, q_stride] (heads ordered q, k, v; nothing rotated yet; left as it is), cos_t / sin_t the angle tables
+// [positions, dh / 2].  write_kv = 1: the new token's key (rotated) and value go into kc / vc; 0: they are there
+// already (a layer that reads another layer's cache) and only the queries are rotated.
+int tb_attention_decode_rope_bf16(const void* qkv, void* out, void* kc, void* vc, const int* tok_seq, const int* tok_pos,
+                                  const int* page_table, float* partial, unsigned* done, const float* cos_t,
+                                  const float* sin_t, int nt, int max_pages, int q_stride, int nh, int nkvh, int dh,
+                                  int splits, int cache_pages, int half_pairing, int write_kv, float scale,
+                                  cudaStream_t s) {
+    if (q_stride < (nh + 2 * nkvh) * dh) return TB_ERR_ARG;
+    return decode_mma(qkv, out, kc, vc, tok_seq, tok_pos, page_table, partial, done, cos_t, sin_t, nt, max_pages,
+                      q_stride, nh, nkvh, dh, splits, cache_pages, half_pairing, write_kv ? 1 : 0, true, scale, s);
+}
+}
+
 // replayable from C++ (tape.h)
 #include "tape.h"
 TB_TAPE_REGISTER(tb_attention_decode_mma_bf16)
+TB_TAPE_REGISTER(tb_attention_decode_rope_bf16)

@@ -35,6 +35,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_attention_tc_bf16": "pppppppppiiiiiiiif",
     "tb_gemm_tc_bf16": "ppppiiiiiiii", "tb_gather_rows_bf16": "pppii",
     "tb_attention_decode_mma_bf16": "pppppppppiiiiiiiif",
+    "tb_attention_decode_rope_bf16": "pppppppppppiiiiiiiiiif",
     "tb_router_f32": "pppppppppiiii", "tb_router_bf16": "pppppppppiiii",
     "tb_router_rows_bf16": "pppppppppiiii",
     "tb_moe_dispatch": "ppppiii",

@@ -18,6 +18,7 @@ from .spec import PartSpec
 
 USE_TCGEN05 = True     # prompts: the tcgen05 kernel before the mma.sync one
 USE_DECODE_RING = True  # decoding: the kernel with a ring of cache pages (TMA, tensor cores) before the register-staged one
+FUSE_DECODE_ROPE = True # decoding: that kernel also rotates q and k and writes the cache (no rotary kernel)
 
 
 @MIXERS.register("attention")
@@ -83,11 +84,14 @@ class Attention(Mixer):
                 self.position.apply(ctx, qkv, self.nh, self.nkvh, self.dh)     # any other: by its own means
             cos, sin = ctx.identity_rotation(self.dh)
             half = 0
+        o = ctx.scratch("attn.o", (nt, self.nh * self.dh), self.dtype)
+        if ctx.decode and self._decode_fused(ctx, qkv, o, cache, table, nt, cos, sin, half):
+            matmul_nt(o, self.weights["wo"], out)      # rotation and cache write happened inside the attention kernel
+            return
         kc, vc = (cache.k, cache.v) if cache.writable else (None, None)
         lib.call("tb_rope_cache_" + sfx, lib.ptr(qkv), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos),
                  lib.ptr(table), ctx.max_pages, lib.ptr(cos), lib.ptr(sin), lib.ptr(kc), lib.ptr(vc),
                  nt, self.nh, self.nkvh, self.dh, half)
-        o = ctx.scratch("attn.o", (nt, self.nh * self.dh), self.dtype)
         if ctx.decode and self._decode_kernel(ctx, qkv, o, cache, table, nt, sfx):
             matmul_nt(o, self.weights["wo"], out)
             return
@@ -119,10 +123,13 @@ class Attention(Mixer):
                  splits, self.scale)
         matmul_nt(o, self.weights["wo"], out)
 
-    def _decode_kernel(self, ctx, qkv, o, cache, table, nt, sfx) -> bool:
-        """One token per sequence: the kernel that streams the cache.  False if it refuses the head size."""
+    def _ring(self) -> bool:
+        """Whether decoding runs the kernel with a ring of cache pages (TMA, tensor cores)."""
+        return USE_DECODE_RING and self.dtype == torch.bfloat16 and self.dh in (64, 128)
+
+    def _decode_plan(self, ctx, nt, ring):
+        """Slices of the keys, and the scratch they need: (splits, partial results, counters of finished slices)."""
         group = self.nh // self.nkvh
-        ring = USE_DECODE_RING and self.dtype == torch.bfloat16 and self.dh in (64, 128)
         gc = 16 if ring else 1 if group == 1 else 2 if group == 2 else 4       # query heads of a group per block
         blocks = nt * self.nkvh * ((group + gc - 1) // gc)
         # Slices of the keys so that the blocks fill the GPU: as many blocks as are resident at once for the kernel
@@ -131,12 +138,30 @@ class Attention(Mixer):
         # alone, since a captured graph keeps it for as long as the sequences grow (the kernels cut short sequences
         # into fewer slices by themselves).
         splits = int(max(1, min(32, ((2 if ring else 8) * ctx.engine.sm_count) // blocks)))
-        partial = None
+        partial = done = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
+            if ring:    # the block that finishes a head group's last slice merges them
+                done = ctx.scratch("attn.done", (nt * self.nh,), torch.int32, zero=True)
+        return splits, partial, done
+
+    def _decode_fused(self, ctx, qkv, o, cache, table, nt, cos, sin, half) -> bool:
+        """One token per sequence, straight from the q-k-v product: the ring kernel also rotates the queries and the
+        new key and writes key and value into the cache.  False (and nothing done) if it refuses."""
+        if not (self._ring() and FUSE_DECODE_ROPE):
+            return False
+        splits, partial, done = self._decode_plan(ctx, nt, True)
+        return lib.try_call("tb_attention_decode_rope_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                            lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), lib.ptr(done),
+                            lib.ptr(cos), lib.ptr(sin), nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh,
+                            splits, cache.k.shape[0], half, 1 if cache.writable else 0, self.scale)
+
+    def _decode_kernel(self, ctx, qkv, o, cache, table, nt, sfx) -> bool:
+        """One token per sequence, queries rotated and the cache written: the kernels that stream the cache.  False if
+        they refuse the head size."""
+        ring = self._ring()
+        splits, partial, done = self._decode_plan(ctx, nt, ring)
         if ring:
-            # counters of finished slices: the block that finishes a head group's last slice merges them
-            done = ctx.scratch("attn.done", (nt * self.nh,), torch.int32, zero=True) if splits > 1 else None
             if lib.try_call("tb_attention_decode_mma_bf16", lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k),
                             lib.ptr(cache.v), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table),
                             lib.ptr(partial), lib.ptr(done), nt, ctx.max_pages, self.qkv_width, self.nh, self.nkvh,
