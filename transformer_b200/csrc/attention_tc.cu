@@ -56,6 +56,30 @@ __device__ __forceinline__ uint64_t umma_desc_strides(uint32_t smem_addr, uint32
     return d;
 }
 
+// 32 columns of this thread's lane without waiting for them (tcgen05.wait::ld comes before their first use)
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Two floats in one 64-bit register, for the packed arithmetic of sm_100 (fma.rn.f32x2, add.rn.f32x2).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -251,13 +275,14 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
             if (!ok) break;
             float s[AT_BN];
             {
-                float lo[32], hi[32];
-                tmem_ld32(tmem_s + (j & 1) * AT_BN + lane_sel, lo);
-                tmem_ld32(tmem_s + (j & 1) * AT_BN + lane_sel + 32, hi);
+                uint32_t lo[32], hi[32];                 // both halves asked for, one wait
+                tmem_ld32_nowait(tmem_s + (j & 1) * AT_BN + lane_sel, lo);
+                tmem_ld32_nowait(tmem_s + (j & 1) * AT_BN + lane_sel + 32, hi);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    s[i] = lo[i];
-                    s[32 + i] = hi[i];
+                    s[i] = __uint_as_float(lo[i]);
+                    s[32 + i] = __uint_as_float(hi[i]);
                 }
             }
             // The softmax warps are bound by instruction issue and by the exponential unit, so the row is
@@ -270,10 +295,14 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
                 for (int i = 0; i < AT_BN; ++i)
                     if (key0 + i > pos_r) s[i] = -INFINITY;
             }
-            float mx = -INFINITY;
+            // two chains of three-input maxima: 32 instructions for the 64 scores
+            float mx = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < AT_BN; ++i) mx = fmaxf(mx, s[i]);
-            mx *= a.scale_log2e;
+            for (int i = 0; i < AT_BN; i += 4) {
+                asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(s[i]), "f"(s[i + 1]));
+                asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(s[i + 2]), "f"(s[i + 3]));
+            }
+            mx = fmaxf(mx, mx1) * a.scale_log2e;
             // raise the maximum only when it has grown by more than 8; then O must be rescaled
             const bool raise = mx > m_used + 8.0f;          // also true for the first visible keys (m_used = -inf)
             const float m_new = raise ? mx : m_used;
@@ -283,18 +312,31 @@ __global__ void __launch_bounds__(AT_THREADS) attention_tc_kernel(const __grid_c
             // computed BEFORE waiting for the previous tile's P V: the exponentials overlap that product,
             // only the stores below come after it
             uint32_t pk[AT_BN / 2];
-            float psum0 = 0.f, psum1 = 0.f;
+            // two scores at a time through the packed forms of multiply-add and add (half the instructions)
+            const uint64_t sc2 = pack_f32x2(a.scale_log2e, a.scale_log2e), nm2 = pack_f32x2(neg_m, neg_m);
+            uint64_t psum_a = 0ull, psum_b = 0ull;              // two pairs of +0.0f
 #pragma unroll
-            for (int i = 0; i < AT_BN; i += 2) {
-                float p0, p1;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(s[i], a.scale_log2e, neg_m)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(s[i + 1], a.scale_log2e, neg_m)));
-                psum0 += p0;
-                psum1 += p1;
-                __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1);
-                pk[i / 2] = *reinterpret_cast<uint32_t*>(&hp);
+            for (int i = 0; i < AT_BN; i += 4) {
+                uint64_t t0, t1;
+                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t0) : "l"(pack_f32x2(s[i], s[i + 1])), "l"(sc2), "l"(nm2));
+                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t1) : "l"(pack_f32x2(s[i + 2], s[i + 3])), "l"(sc2), "l"(nm2));
+                float e0, e1, e2, e3, p0, p1, p2, p3;
+                unpack_f32x2(t0, e0, e1);
+                unpack_f32x2(t1, e2, e3);
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(e0));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(e1));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p2) : "f"(e2));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p3) : "f"(e3));
+                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(psum_a) : "l"(pack_f32x2(p0, p1)));
+                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(psum_b) : "l"(pack_f32x2(p2, p3)));
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+                pk[i / 2] = *reinterpret_cast<uint32_t*>(&h0);
+                pk[i / 2 + 1] = *reinterpret_cast<uint32_t*>(&h1);
             }
-            l_run = l_run * rescale + (psum0 + psum1);
+            float ps0, ps1, ps2, ps3;
+            unpack_f32x2(psum_a, ps0, ps1);
+            unpack_f32x2(psum_b, ps2, ps3);
+            l_run = l_run * rescale + ((ps0 + ps1) + (ps2 + ps3));
             // O may only be touched once the previous tile's P V is done (P itself goes where this tile's S was,
             // which nothing reads any more: no wait for that)
             const bool touch_o = __any_sync(0xffffffffu, rescale != 1.0f) && j > 0;
