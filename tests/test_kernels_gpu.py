@@ -548,10 +548,13 @@ def test_gemm_tc_grouped_swiglu_and_down(E, k, nt, d, di):
     assert worst <= 2.0 ** -7
 
 
-@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 64), (8, 8, 128), (6, 1, 128)])
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 64), (8, 8, 128), (6, 1, 128), (4, 2, 16), (3, 1, 48), (6, 3, 80), (4, 1, 96),
+                                        (2, 2, 112), (2, 1, 144), (4, 2, 160), (2, 1, 192), (3, 3, 208), (2, 1, 240),
+                                        (4, 2, 256)])
 def test_attention_prompt_kernel(nh, nkvh, dh):
     """The tensor-core prompt kernel on a ragged batch: prompts from zero (shorter and longer than a
-    tile, not multiples of 64), a continued prompt whose cache already holds 130 tokens, a single token."""
+    tile, not multiples of 64), a continued prompt whose cache already holds 130 tokens, a single token; at head sizes
+    from 16 to 256 (rows of shared memory padded to a multiple of 64 values)."""
     lib = _lib()
     dtype = torch.bfloat16
     tq = lib.attention_prefill_tile_tokens()
@@ -569,7 +572,7 @@ def test_attention_prompt_kernel(nh, nkvh, dh):
     assert not lib.try_call("tb_attention_prefill_bf16", c["q"].data_ptr(), out.data_ptr(), c["kc"].data_ptr(),
                             c["vc"].data_ptr(), c["tile_seq"].data_ptr(), c["tile_t0"].data_ptr(),
                             c["tile_nq"].data_ptr(), c["tok_pos"].data_ptr(), c["table"].data_ptr(), c["tiles"],
-                            c["max_pages"], nh * 48, nh, c["nkvh"], 48, 1.0)
+                            c["max_pages"], nh * 40, nh, c["nkvh"], 40, 1.0)
 
 
 @pytest.mark.parametrize("nh,nkvh,dh", [(4, 2, 64), (8, 8, 128), (6, 1, 128)])

@@ -41,9 +41,10 @@ class Attention(Mixer):
         self.scale = 1.0 / math.sqrt(self.dh)
         # query tiles this mixer asks the step to plan: the general kernel's, and the prompt kernel's
         self.general_tile = lib.attention_tile_tokens(self.nh, self.nkvh)
-        self.prompt_tile = lib.attention_prefill_tile_tokens() if (dtype == torch.bfloat16 and self.dh in (64, 128)) else 0
-        self.tc_tile = lib.attention_tc_tile_tokens() if self.prompt_tile else 0
-        self.tile_sizes = [self.general_tile] + ([self.prompt_tile, self.tc_tile] if self.prompt_tile else [])
+        # bfloat16 prompts: the mma.sync kernel takes every head size, the tcgen05 kernel heads of 64 and 128
+        self.prompt_tile = lib.attention_prefill_tile_tokens() if dtype == torch.bfloat16 else 0
+        self.tc_tile = lib.attention_tc_tile_tokens() if (self.prompt_tile and self.dh in (64, 128)) else 0
+        self.tile_sizes = [t for t in (self.general_tile, self.prompt_tile, self.tc_tile) if t]
 
     @property
     def graph_safe(self) -> bool:
