@@ -595,7 +595,7 @@ def test_attention_tcgen05_kernel(nh, nkvh, dh):
 
 
 @pytest.mark.parametrize("nh,nkvh,dh", [(4, 4, 64), (8, 8, 128), (12, 2, 64), (20, 2, 128), (3, 1, 128), (32, 8, 128),
-                                        (16, 1, 64), (40, 2, 128), (51, 3, 64)])
+                                        (16, 1, 64), (40, 2, 128), (51, 3, 64), (6, 2, 192), (3, 3, 256), (8, 2, 256)])
 def test_attention_decode_on_tensor_cores(nh, nkvh, dh):
     """The decode kernel whose products run as mma.sync with a group's query heads as rows: groups of 1, 3, 4, 6, 10,
     exactly 16, 17 and 20 heads (more than 16 take two blocks); contexts of one token, exactly one page, a page and a
@@ -622,7 +622,8 @@ def test_attention_decode_on_tensor_cores(nh, nkvh, dh):
 
 
 @pytest.mark.parametrize("pairing", ["adjacent", "half"])
-@pytest.mark.parametrize("nh,nkvh,dh", [(4, 4, 64), (8, 2, 128), (12, 2, 64), (40, 2, 128), (3, 1, 128)])
+@pytest.mark.parametrize("nh,nkvh,dh", [(4, 4, 64), (8, 2, 128), (12, 2, 64), (40, 2, 128), (3, 1, 128), (6, 2, 192),
+                                        (4, 1, 256)])
 def test_decode_attention_that_also_rotates_and_writes_the_cache(nh, nkvh, dh, pairing):
     """The fused form against the two kernels it stands for (rotary kernel, then the attention over the finished
     cache), from the same unrotated q-k-v rows: the same output, the same cache rows written, q-k-v left alone; with

@@ -1,4 +1,4 @@
-// Attention for decoding, bfloat16, head sizes 64 and 128: the cache pages come by TMA, the products run on the
+// Attention for decoding, bfloat16, head sizes 64, 128, 192 and 256: the cache pages come by TMA, the products run on the
 // tensor cores.
 //
 // Same mathematics and the same cut of the work as attention_decode.cu (a block = one query token x one key/value
@@ -183,7 +183,8 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
         // Fused: the angles of this token's position were there before the step began; they are read before the
         // wait, the q-k-v row's new key and value (by the warp that owns their row of the last page) right after it.
         float ang[FUSE ? KS * 4 : 1];                     // this thread's cosines and sines for the queries
-        float pc[2] = {1.f, 1.f}, ps[2] = {0.f, 0.f};     // and for pairs lane, lane + 32 of the new key
+        constexpr int NPL = (DH / 2 + 31) / 32;           // pairs of the new key per lane: lane, lane + 32, ...
+        float pc[NPL], ps[NPL];                           // their cosines and sines
         const bool patcher = FUSE && a.patch && p_hi == n_pages && np > 0 && warp == (pos % TB_PAGE) / 16;
         if (FUSE) {
             const float* cs = a.cos_t + (size_t)pos * (DH / 2);
@@ -211,7 +212,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
             }
             if (patcher) {
 #pragma unroll
-                for (int u = 0; u < 2; ++u)
+                for (int u = 0; u < NPL; ++u)
                     if (lane + 32 * u < DH / 2) {
                         pc[u] = cs[lane + 32 * u];
                         ps[u] = sn[lane + 32 * u];
@@ -219,12 +220,12 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
             }
         }
         asm volatile("griddepcontrol.wait;" ::: "memory");     // the queries come from the kernel before
-        float kx0[2] = {0.f, 0.f}, kx1[2] = {0.f, 0.f};
+        float kx0[NPL], kx1[NPL];
         uint4 vnew = make_uint4(0u, 0u, 0u, 0u);
         if (patcher) {
             const __nv_bfloat16* kn = a.q + (size_t)t * a.q_stride + (size_t)(a.nh + g) * DH;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < NPL; ++u) {
                 const int p = lane + 32 * u;
                 if (p < DH / 2) {
                     kx0[u] = __bfloat162float(kn[a.half_pairing ? p : 2 * p]);
@@ -296,7 +297,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
                 const bool writer = blockIdx.y % chunks == 0;
                 const size_t at = (((size_t)pt[n_pages - 1] * a.nkvh + g) * TB_PAGE + row) * DH;
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
+                for (int u = 0; u < NPL; ++u) {
                     const int p = lane + 32 * u;
                     if (p < half) {
                         const int d0 = a.half_pairing ? p : 2 * p, d1 = a.half_pairing ? p + half : 2 * p + 1;
@@ -453,8 +454,9 @@ template <int DH, bool FUSE>
 static int decode_mma_launch(const CUtensorMap& mk, const CUtensorMap& mv, DecodeMmaArgs a, int nt, cudaStream_t s) {
     const size_t stage = (size_t)2 * TB_PAGE * DH * 2;
     const size_t tail = 2 * DM_MAX_STAGES * 8 + (size_t)2 * DM_WARPS * DM_HEADS * sizeof(float);
-    // about half of an SM's shared memory per block: two blocks per SM keep their rings in flight together
-    int stages = (int)((110 * 1024 - 1024 - tail) / stage);
+    // about half of an SM's shared memory per block: two blocks per SM keep their rings in flight together; heads
+    // above 128 leave room for one block only (registers), which then takes most of the shared memory
+    int stages = (int)(((DH <= 128 ? 110 : 200) * 1024 - 1024 - tail) / stage);
     if (stages > DM_MAX_STAGES) stages = DM_MAX_STAGES;
     if (stages < 2) stages = 2;
     a.stages = stages;
@@ -481,7 +483,7 @@ static int decode_mma(const void* q, void* out, void* kc, void* vc, const int* t
     if (nh <= 0 || nkvh <= 0 || nh % nkvh || splits < 1 || cache_pages <= 0) return TB_ERR_ARG;
     if (splits > 1 && !partial) return TB_ERR_ARG;
     if (fuse && !(cos_t && sin_t)) return TB_ERR_ARG;
-    if (dh != 64 && dh != 128) return TB_ERR_UNSUPPORTED;
+    if (dh != 64 && dh != 128 && dh != 192 && dh != 256) return TB_ERR_UNSUPPORTED;
     if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) & 15)) return TB_ERR_UNSUPPORTED;
     if (fuse && (((uintptr_t)cos_t | (uintptr_t)sin_t) & 7)) return TB_ERR_UNSUPPORTED;
     if (nt <= 0) return nt == 0 ? 0 : TB_ERR_ARG;
@@ -497,8 +499,16 @@ static int decode_mma(const void* q, void* out, void* kc, void* vc, const int* t
     DecodeMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_seq, tok_pos, page_table, partial, done, err,
                     max_pages, q_stride, nh, nkvh, splits, 0, scale * 1.4426950408889634f,
                     cos_t, sin_t, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, half_pairing, patch};
-    if (fuse) rc = dh == 64 ? decode_mma_launch<64, true>(mk, mv, a, nt, s) : decode_mma_launch<128, true>(mk, mv, a, nt, s);
-    else rc = dh == 64 ? decode_mma_launch<64, false>(mk, mv, a, nt, s) : decode_mma_launch<128, false>(mk, mv, a, nt, s);
+    switch (dh + (fuse ? 1 : 0)) {
+        case 64: rc = decode_mma_launch<64, false>(mk, mv, a, nt, s); break;
+        case 65: rc = decode_mma_launch<64, true>(mk, mv, a, nt, s); break;
+        case 128: rc = decode_mma_launch<128, false>(mk, mv, a, nt, s); break;
+        case 129: rc = decode_mma_launch<128, true>(mk, mv, a, nt, s); break;
+        case 192: rc = decode_mma_launch<192, false>(mk, mv, a, nt, s); break;
+        case 193: rc = decode_mma_launch<192, true>(mk, mv, a, nt, s); break;
+        case 256: rc = decode_mma_launch<256, false>(mk, mv, a, nt, s); break;
+        default: rc = decode_mma_launch<256, true>(mk, mv, a, nt, s); break;
+    }
     if (rc) return rc;
     if (splits > 1 && !done) {
         dim3 grid(nt, nh);

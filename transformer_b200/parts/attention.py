@@ -126,7 +126,7 @@ class Attention(Mixer):
 
     def _ring(self) -> bool:
         """Whether decoding runs the kernel with a ring of cache pages (TMA, tensor cores)."""
-        return USE_DECODE_RING and self.dtype == torch.bfloat16 and self.dh in (64, 128)
+        return USE_DECODE_RING and self.dtype == torch.bfloat16 and self.dh in (64, 128, 192, 256)
 
     def _decode_plan(self, ctx, nt, ring):
         """Slices of the keys, and the scratch they need: (splits, partial results, counters of finished slices)."""
