@@ -19,6 +19,7 @@ from .spec import PartSpec
 USE_TCGEN05 = True     # prompts: the tcgen05 kernel before the mma.sync one
 USE_DECODE_RING = True  # decoding: the kernel with a ring of cache pages (TMA, tensor cores) before the register-staged one
 FUSE_DECODE_ROPE = True # decoding: that kernel also rotates q and k and writes the cache (no rotary kernel)
+RING_BLOCKS_PER_SM = 2  # decoding: the keys are sliced until that kernel has this many blocks per SM
 
 
 @MIXERS.register("attention")
@@ -134,11 +135,11 @@ class Attention(Mixer):
         gc = 16 if ring else 1 if group == 1 else 2 if group == 2 else 4       # query heads of a group per block
         blocks = nt * self.nkvh * ((group + gc - 1) // gc)
         # Slices of the keys so that the blocks fill the GPU: as many blocks as are resident at once for the kernel
-        # that keeps a ring of pages in shared memory (two per SM: measured best at batch 1 to 16, also with lengths
-        # that differ 16-fold), eight times the SMs for the register-staged one.  A function of the batch's shape
+        # that keeps a ring of pages in shared memory (two per SM: measured best in the step at batch 1 to 16, also with
+        # lengths that differ 16-fold; alone, the kernel would rather have one per SM), eight times the SMs for the register-staged one.  A function of the batch's shape
         # alone, since a captured graph keeps it for as long as the sequences grow (the kernels cut short sequences
         # into fewer slices by themselves).
-        splits = int(max(1, min(32, ((2 if ring else 8) * ctx.engine.sm_count) // blocks)))
+        splits = int(max(1, min(32, ((RING_BLOCKS_PER_SM if ring else 8) * ctx.engine.sm_count) // blocks)))
         partial = done = None
         if splits > 1:
             partial = ctx.scratch("attn.partial", (nt, self.nh, splits, self.dh + 2), torch.float32)
