@@ -25,7 +25,7 @@
 // The fused form (FUSE) also does what the rotary kernel does for a decode step, so that a layer has one launch
 // less: the queries are rotated as they are loaded into registers; the new token's key (rotated) and value are taken
 // from the q-k-v product's result, laid over the row of the last page in shared memory that TMA brought in its old
-// state, and written to the cache by the block of the group's first 16 heads.  The producer then waits for nothing.
+// state, and written to the cache by the block of the group's first 16 heads.
 //
 // Each of the four arithmetic warps takes 16 of a page's 64 keys and keeps a running (max, sum, O) of its own; they
 // are merged once at the end, in the ring's memory.  With the keys in slices, the block that finishes a (token, head
@@ -98,7 +98,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
                             const DecodeMmaArgs a) {
     // The next kernel may start launching at once.  This one waits for the kernel before it (which wrote the
     // step's queries and the newest key and value) as late as it can: page numbers, positions and every cache
-    // page but the sequence's last were written before the step began, so the ring is filled meanwhile.
+    // page but the sequence's last two were written long before the step began, so the ring is filled meanwhile.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int KS = DH / 16;                         // k-steps of Q.K^T
     constexpr int DT = DH / 8;                          // 8-channel tiles of O
@@ -155,8 +155,11 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap mk, const __grid
             if (lane == 0) {
                 if (i >= S) ok = mbar_wait(empty_bar(s), ((i / S) - 1) & 1, a.error, 25);
                 if (ok) {
-                    // the page a kernel of this step wrote to (fused: this block lays the new row over it itself)
-                    if (!(FUSE && a.patch) && !waited && p_lo + i == n_pages - 1) {
+                    // The sequence's last two pages hold what this step and the 64 or more steps before it
+                    // wrote: they are asked for after the wait.  Older pages were written so many launches ago
+                    // that their writers cannot still be running (a chain of dependent launches is no deeper than
+                    // the grids the device holds at once), and are fetched before it.
+                    if (!waited && p_lo + i >= n_pages - 2) {
                         asm volatile("griddepcontrol.wait;" ::: "memory");
                         waited = true;
                     }
