@@ -20,7 +20,7 @@
 // A block covers 16 * WN output columns of one group.  WK warps split K (warp w takes the 32-wide
 // k-steps w, w + WK, ...: neighbouring warps read neighbouring 64-byte pieces of a weight row) and
 // add their partial sums through shared memory; long rows use 8 x 1 warps, short ones (an expert's
-// down projection) 2 x 4.  Rows are taken 8 * NT at a time.  What bounds the kernel is the number of
+// down projection) 2 x 1.  Rows are taken 8 * NT at a time.  What bounds the kernel is the number of
 // bytes in flight, so every thread issues UNR k-steps of loads before it multiplies any of them.
 // (Measured and dropped: staging the weights through shared memory with cp.async, persistent or
 // not; cp.async.bulk.prefetch.L2 of the block's weight rows; a tcgen05 variant with the weights as
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
     constexpr int NMAT = DUAL ? 2 : 1;
     __shared__ float red[WN][WK][NMAT][ROWS][SK_COLS + 1];
 
-    __shared__ int list[WK * WN * 32];      // with row_group: the rows of this block's group
+    __shared__ int list[SK_WARPS * 32];     // with row_group: the rows of this block's group
     __shared__ unsigned list_mask[WK * WN];
 
     const int g_idx = blockIdx.y;
@@ -130,20 +130,25 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
     int row_lo = 0, row_hi = a.M;
     const bool listed = a.row_group != nullptr;
     if (listed) {
-        // M <= threads: thread m looks at row m; rows keep their order inside the group
-        const int m = threadIdx.x;
-        const bool mine = m < a.M && a.row_group[m] == g_idx;
-        const unsigned mask = __ballot_sync(0xffffffffu, mine);
-        if (lane == 0) list_mask[warp] = mask;
-        __syncthreads();
-        int before = 0, total = 0;
-        for (int w = 0; w < WK * WN; ++w) {
-            const int c = __popc(list_mask[w]);
-            if (w < warp) before += c;
-            total += c;
+        // a thread looks at one row per round of the block's threads (M <= SK_WARPS * 32, the size of the list);
+        // rows keep their order inside the group
+        int total = 0;
+        for (int base = 0; base < a.M; base += WK * WN * 32) {
+            const int m = base + threadIdx.x;
+            const bool mine = m < a.M && a.row_group[m] == g_idx;
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (lane == 0) list_mask[warp] = mask;
+            __syncthreads();
+            int before = 0, round = 0;
+            for (int w = 0; w < WK * WN; ++w) {
+                const int c = __popc(list_mask[w]);
+                if (w < warp) before += c;
+                round += c;
+            }
+            if (mine) list[total + before + __popc(mask & ((1u << lane) - 1u))] = m;
+            total += round;
+            __syncthreads();
         }
-        if (mine) list[before + __popc(mask & ((1u << lane) - 1u))] = m;
-        __syncthreads();
         row_hi = total;
     } else if (a.group_offsets) {
         row_lo = a.group_offsets[g_idx];
@@ -245,7 +250,7 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
 template <int NT, bool DUAL, typename TY>
 static int skinny_launch_shape(const SkinnyArgs& a, cudaStream_t s) {
     // long rows: all 8 warps of a block share 16 columns and split K;
-    // short rows (an expert's down projection): 4 column groups x 2 warps on K
+    // short rows (an expert's down projection): 2 warps on K
     if (a.K >= 2048) {
         constexpr int WK = 8, WN = 1, UNR = NT >= 4 ? 2 : 4;
         dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
@@ -256,7 +261,11 @@ static int skinny_launch_shape(const SkinnyArgs& a, cudaStream_t s) {
         else
             TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR>), grid, WK * WN * 32, 0, s, a);
     } else {
-        constexpr int WK = 2, WN = 4, UNR = NT >= 4 ? 2 : 4;
+        // 16 columns per block, as for long rows: few sequences touch few experts, and the smaller the pieces
+        // of their weights, the more evenly they fall on the SMs (with 4 x 16 columns per block the whole decode
+        // step at batch 8 took 2.4 % longer; 4 or 1 warps on K, or 8 loads ahead, are slower too).  Tried on the
+        // gate/up pair as well (8 gate and 8 up rows per tile, half the bytes per block): no gain.
+        constexpr int WK = 2, WN = 1, UNR = NT >= 4 ? 2 : 4;
         dim3 grid((a.N + SK_COLS * WN - 1) / (SK_COLS * WN), a.G);
         TB_LAUNCH((gemm_skinny_kernel<NT, DUAL, TY, WK, WN, UNR>), grid, WK * WN * 32, 0, s, a);
     }
